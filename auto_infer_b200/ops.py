@@ -1,0 +1,187 @@
+"""Tensor-level wrappers over the C ABI.  Each function takes CUDA tensors,
+passes raw pointers and the current stream to the library and returns torch
+tensors.  CPU tensors are rejected: there is no host implementation."""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import DecodePlanInfo
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError(
+                "auto_infer_b200 operators run on CUDA tensors only (no CPU fallback); "
+                f"got a tensor on {t.device}")
+
+
+_status_words: dict = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 word the kernels OR fault bits into."""
+    key = torch.device(device).index or 0
+    if key not in _status_words:
+        _status_words[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _status_words[key]
+
+
+def read_status(device, clear: bool = True) -> int:
+    """Synchronising read of the device status word (0 = no fault seen)."""
+    word = status_word(device)
+    value = int(word.item())
+    if clear and value:
+        word.zero_()
+    return value
+
+
+def sm_count(device=None) -> int:
+    if device is not None:
+        with torch.cuda.device(device):
+            return _lib.load().b200_sm_count()
+    return _lib.load().b200_sm_count()
+
+
+# --------------------------------------------------------------------------- #
+def reshape_and_cache(key: torch.Tensor, value: Optional[torch.Tensor],
+                      key_cache: torch.Tensor, value_cache: Optional[torch.Tensor],
+                      slot_mapping: torch.Tensor) -> None:
+    """cache[slot // bs, slot % bs] = x[t]; replaces ``write_kv``
+    (auto_infer/layers/attention/base.py:41-45).  key (T, Hkv, Dk) may be a
+    strided view as long as each token row is contiguous."""
+    _need_cuda(key, value, key_cache, value_cache, slot_mapping)
+    lib = _lib.load()
+    t, n_kv, k_dim = key.shape
+    if t == 0:
+        return
+    if key.stride(2) != 1 or key.stride(1) != k_dim:
+        key = key.contiguous()
+    if not key_cache.is_contiguous():
+        raise ValueError("key_cache must be contiguous")
+    num_blocks, block_size = key_cache.shape[0], key_cache.shape[1]
+    v_ptr = vc_ptr = None
+    v_dim = 0
+    v_stride = 0
+    if value is not None:
+        v_dim = value.shape[2]
+        if value.stride(2) != 1 or value.stride(1) != v_dim:
+            value = value.contiguous()
+        if value_cache is None or not value_cache.is_contiguous():
+            raise ValueError("value_cache must be a contiguous tensor when value is given")
+        v_ptr, vc_ptr, v_stride = value.data_ptr(), value_cache.data_ptr(), value.stride(0)
+    if slot_mapping.dtype != torch.int32:
+        slot_mapping = slot_mapping.to(torch.int32)
+    slot_mapping = slot_mapping.contiguous()
+    with torch.cuda.device(key.device):
+        rc = lib.b200_reshape_and_cache(
+            key.data_ptr(), v_ptr, key_cache.data_ptr(), vc_ptr, slot_mapping.data_ptr(),
+            t, n_kv, k_dim, v_dim, key.stride(0), v_stride, block_size, num_blocks,
+            status_word(key.device).data_ptr(), _stream_ptr(key.device))
+    _lib.check(rc, "b200_reshape_and_cache")
+
+
+# --------------------------------------------------------------------------- #
+class DecodePlan:
+    """Host plan + device copy + workspace for one step of split-KV decode.
+    Built once per step from the two host length lists and shared by all layers
+    (the reference hands the same lists to its vendor op per layer,
+    auto_infer/layers/attention/gqa.py:91-92)."""
+
+    def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_q_heads: int,
+                 num_kv_heads: int, device, head_dim: int = 128, num_ctas: Optional[int] = None,
+                 causal_base: Optional[Sequence[int]] = None):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("DecodePlan needs a CUDA device (no CPU fallback)")
+        self.num_seqs = len(cu_seqlens_q)
+        self.num_q_heads, self.num_kv_heads, self.head_dim = num_q_heads, num_kv_heads, head_dim
+        self.num_ctas = int(num_ctas) if num_ctas else sm_count(self.device)
+        nbytes = lib.b200_decode_plan_bytes(self.num_seqs, num_kv_heads, self.num_ctas)
+        self.host = torch.empty(nbytes // 4, dtype=torch.int32, pin_memory=True)
+        cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
+        kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
+        base_ptr = None
+        if causal_base is not None:
+            base = torch.tensor(list(causal_base), dtype=torch.int32)
+            base_ptr = base.data_ptr()
+        self.info = DecodePlanInfo()
+        rc = lib.b200_decode_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, self.num_seqs,
+                                  num_q_heads, num_kv_heads, self.num_ctas,
+                                  self.host.data_ptr(), nbytes, ctypes.byref(self.info))
+        _lib.check(rc, "b200_decode_plan")
+        used = max(int(self.info.plan_ints), 16)
+        self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
+        self.dev.copy_(self.host[:used], non_blocking=True)
+        ws = (self.info.num_partials * (16 * head_dim + 16)) * 4 + 256
+        self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
+
+    @property
+    def skipped_seqs(self) -> int:
+        return int(self.info.skipped_seqs)
+
+
+def paged_decode_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                     block_table: torch.Tensor, plan: DecodePlan, scale: float,
+                     out: Optional[torch.Tensor] = None, out_f32: bool = False,
+                     lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged GQA attention for decode-shaped rows (q_len * group <= 16).
+    Replaces ``paged_fia`` (auto_infer/layers/attention/base.py:48-61).  Rows of
+    sequences the plan skipped are left untouched in ``out``."""
+    _need_cuda(q, key_cache, value_cache, block_table)
+    lib = _lib.load()
+    t, n_q, d = q.shape
+    if q.stride(2) != 1 or q.stride(1) != d:
+        q = q.contiguous()
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("KV caches must be contiguous (num_blocks, block_size, Hkv, D)")
+    num_blocks, block_size, n_kv, _ = key_cache.shape
+    if block_table.dtype != torch.int32:
+        block_table = block_table.to(torch.int32)
+    if block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+    if out is None:
+        out = torch.empty(t, n_q, d, dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
+    elif not out.is_contiguous():
+        raise ValueError("out must be contiguous")
+    with torch.cuda.device(q.device):
+        rc = lib.b200_paged_decode_gqa(
+            q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
+            num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+            plan.dev.data_ptr(), ctypes.byref(plan.info), n_q, n_kv, d, float(scale),
+            plan.workspace.data_ptr(), plan.workspace.numel(), out.data_ptr(),
+            1 if out.dtype == torch.float32 else 0,
+            lse_out.data_ptr() if lse_out is not None else None,
+            status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "b200_paged_decode_gqa")
+    return out
+
+
+def lse_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor,
+                out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
+                lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Merge (R, rows, D) fp32 partial outputs with their (R, rows) fp32 lse.
+    Parts may be strided along dim 0 (e.g. views into an all-gather buffer)."""
+    _need_cuda(o_parts, lse_parts)
+    lib = _lib.load()
+    r, rows, d = o_parts.shape
+    if o_parts.stride(2) != 1 or o_parts.stride(1) != d or lse_parts.stride(1) != 1:
+        raise ValueError("each part must be contiguous (rows, D) / (rows,)")
+    if out is None:
+        out = torch.empty(rows, d, dtype=out_dtype, device=o_parts.device)
+    with torch.cuda.device(o_parts.device):
+        rc = lib.b200_lse_combine(
+            o_parts.data_ptr(), lse_parts.data_ptr(), o_parts.stride(0), lse_parts.stride(0),
+            r, rows, d, out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+            lse_out.data_ptr() if lse_out is not None else None, _stream_ptr(o_parts.device))
+    _lib.check(rc, "b200_lse_combine")
+    return out

@@ -1,0 +1,148 @@
+/*
+ * b200_attention.h — C ABI of the B200 (sm_100a) paged-attention library.
+ *
+ * Every entry point takes raw device pointers, plain sizes and a CUDA stream
+ * (passed as void*; NULL = the legacy default stream).  None of them allocates
+ * device memory unless its comment says so; the caller owns inputs, outputs and
+ * workspaces.  Return value: 0 on success, a negative B200_E* code when an
+ * argument is rejected (nothing is launched then).  Faults found on the device
+ * (a block id outside the pool, a slot outside the cache, a wait that ran out)
+ * never trap: the offending access is skipped and a bit is OR-ed into the int32
+ * status word the caller passed (may be NULL).
+ *
+ * The functions replace the two vendor operators auto-infer's attention
+ * backends call, plus the pieces a split / context-parallel run needs:
+ *
+ *   b200_reshape_and_cache      auto_infer/layers/attention/base.py:41-45   (write_kv)
+ *   b200_paged_decode_gqa       auto_infer/layers/attention/base.py:48-61   (paged_fia, q_len*group <= 16)
+ *   b200_paged_prefill_gqa      auto_infer/layers/attention/base.py:48-61   (paged_fia, any q_len)
+ *   b200_mla_decode_absorbed    auto_infer/layers/attention/mla.py:115-120  (paged_fia over the 576-wide latent)
+ *   b200_lse_combine            no vendor counterpart; merges what graph_fia.py:41 calls [o, lse]
+ *   b200_decode_plan*           host-side replacement of the per-step host length lists
+ *                               (auto_infer/worker/model_runner.py:126-136)
+ */
+#ifndef B200_ATTENTION_H_
+#define B200_ATTENTION_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- return codes ------------------------------------------------------ */
+#define B200_OK               0
+#define B200_EINVAL          -1   /* null pointer, negative size, bad stride        */
+#define B200_EUNSUPPORTED    -2   /* shape outside what the kernels are built for   */
+#define B200_EALIGN          -3   /* pointer / stride not aligned as required       */
+#define B200_ECUDA           -4   /* a CUDA runtime / driver call failed            */
+#define B200_ETOOLARGE       -5   /* exceeds a stated fixed capacity                */
+#define B200_EPLAN           -6   /* plan buffer too small or inconsistent          */
+
+/* ---- bits OR-ed into the device status word ------------------------------ */
+#define B200_STATUS_BAD_SLOT      1   /* slot outside [0, num_blocks*block_size)   */
+#define B200_STATUS_BAD_BLOCK     2   /* block id outside [0, num_blocks)          */
+#define B200_STATUS_WAIT_TIMEOUT  4   /* a bounded barrier wait ran out            */
+
+/* Library / build identification: "b200-attention <ver> sm_100a". */
+const char* b200_version(void);
+/* Text of the last rejected call on this thread (never NULL). */
+const char* b200_last_error(void);
+/* Number of SMs of the current device (persistent kernels launch one CTA each). */
+int b200_sm_count(void);
+
+/* ------------------------------------------------------------------------ *
+ * KV-cache slot write.  Replaces write_kv
+ * (auto_infer/layers/attention/base.py:41-45; callers gqa.py:76-79,
+ * mla.py:113,243-245).
+ *   key   (T, Hkv, k_dim) bf16, row t starts at key + t*key_stride (elements)
+ *   value (T, Hkv, v_dim) bf16 or NULL (latent cache stored once)
+ *   caches (num_blocks, block_size, Hkv, dim) bf16, contiguous
+ *   slot_mapping (T,) int32: slot = block*block_size + offset; negative slots
+ *   are skipped silently (padding rows), slots past the pool set BAD_SLOT.
+ * Bit-exact copy. */
+int b200_reshape_and_cache(const void* key, const void* value,
+                           void* key_cache, void* value_cache,
+                           const int32_t* slot_mapping,
+                           int num_tokens, int num_kv_heads, int k_dim, int v_dim,
+                           int64_t key_stride, int64_t value_stride,
+                           int block_size, int num_blocks,
+                           int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Split-KV decode plan (host).  The reference hands the vendor op two host
+ * lists per step (cumulative query lengths, per-sequence kv lengths:
+ * auto_infer/worker/model_runner.py:126-136, forward_context.py:15-16).  Here
+ * the same two lists are turned, once per step and for all layers, into a flat
+ * work list: the 64-token KV tiles of every (sequence, kv head) pair are laid
+ * end to end and cut into num_ctas equal ranges, so every CTA streams the same
+ * number of bytes whatever the length distribution.
+ *
+ * Sequences whose q_len * (Hq/Hkv) exceeds 16 rows are left out (they belong to
+ * b200_paged_prefill_gqa); their count is reported in info->skipped_seqs.
+ *
+ * causal_base may be NULL (then kv_len - q_len is used): key j of sequence b is
+ * visible to its query row i iff j <= causal_base[b] + i.  A context-parallel
+ * rank passes its local kv lengths and a base shifted by its slice offset.
+ */
+typedef struct b200_decode_plan_info {
+  int32_t num_ctas;        /* grid of the decode kernel                         */
+  int32_t num_items;       /* work items (CTA range x (seq, kv head))           */
+  int32_t num_partials;    /* partial (o, lse) records the kernel writes        */
+  int32_t num_multi;       /* (seq, kv head) groups merged by the combine pass  */
+  int32_t total_tiles;     /* 64-token tiles over all groups                    */
+  int32_t skipped_seqs;    /* sequences too wide for the decode kernel          */
+  int32_t plan_ints;       /* int32 words of the plan actually used             */
+  int32_t reserved;
+} b200_decode_plan_info;
+
+/* Upper bounds for sizing buffers before the lengths are known. */
+size_t b200_decode_plan_bytes(int num_seqs, int num_kv_heads, int num_ctas);
+size_t b200_decode_workspace_bytes(int num_seqs, int num_kv_heads, int num_ctas, int head_dim);
+
+int b200_decode_plan(const int32_t* cu_seqlens_q_host, const int32_t* seqlens_kv_host,
+                     const int32_t* causal_base_host,
+                     int num_seqs, int num_q_heads, int num_kv_heads, int num_ctas,
+                     int32_t* plan_host, size_t plan_bytes,
+                     b200_decode_plan_info* info);
+
+/* ------------------------------------------------------------------------ *
+ * Paged GQA decode / MTP-verify attention, q_len * (Hq/Hkv) <= 16 per
+ * sequence.  Replaces paged_fia (auto_infer/layers/attention/base.py:48-61) as
+ * called from GqaFIABackend._attn (gqa.py:81-94) for decode-shaped rows.
+ *   q (T, Hq, 128) bf16, row stride q_stride elements
+ *   caches (num_blocks, block_size, Hkv, 128) bf16; block_size a power of two >= 8
+ *   block_table (B, >= blocks needed) int32, row stride bt_stride
+ *   plan_dev: device copy of the plan built by b200_decode_plan (info by value)
+ *   workspace: b200_decode_workspace_bytes() bytes, 256-byte aligned
+ *   out: (T, Hq, 128) bf16 when out_is_f32 == 0, fp32 otherwise (the fp32 form
+ *        is one context-parallel rank's partial); lse_out (T, Hq) fp32 or NULL
+ * Mask: bottom-right causal (sparse_mode 3 of the vendor op). */
+int b200_paged_decode_gqa(const void* q, int64_t q_stride,
+                          const void* key_cache, const void* value_cache,
+                          int num_blocks, int block_size,
+                          const int32_t* block_table, int64_t bt_stride,
+                          const int32_t* plan_dev, const b200_decode_plan_info* info,
+                          int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                          void* workspace, size_t workspace_bytes,
+                          void* out, int out_is_f32, float* lse_out,
+                          int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Merge n_parts normalised partial results by log-sum-exp:
+ *   o_parts (n_parts, rows, D) fp32, lse_parts (n_parts, rows) fp32 (natural
+ *   log, -inf = empty part)  ->  out (rows, D) bf16 (or fp32 if out_is_f32),
+ *   lse_out (rows) or NULL.
+ * part_stride_o / part_stride_lse are element strides between parts, so the
+ * buffer an all-gather filled with per-rank [o | lse] records can be merged in
+ * place.  Used for context-parallel partials; D must be a multiple of 4. */
+int b200_lse_combine(const float* o_parts, const float* lse_parts,
+                     int64_t part_stride_o, int64_t part_stride_lse,
+                     int n_parts, int64_t rows, int head_dim,
+                     void* out, int out_is_f32, float* lse_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* B200_ATTENTION_H_ */
