@@ -3,7 +3,7 @@
 // HBM-bound: every key/value byte is read exactly once, so the kernel is built
 // around keeping enough loads in flight per SM.  One persistent CTA per SM:
 //   * warp 8 (producer) walks the CTA's work items and streams 64-token K and V
-//     tiles of the (sequence, kv head) pair into a 5-stage shared-memory ring
+//     tiles of the (sequence, kv head) pair into a 6-stage shared-memory ring
 //     with TMA (cp.async.bulk.tensor, 128-byte swizzle), block ids coming from
 //     the block table; it runs ahead across item boundaries, so the ring never
 //     drains between items;
@@ -23,7 +23,13 @@
 namespace b200 {
 
 constexpr int kHeadDim = 128;
-constexpr int kStages = 5;
+// The stage count must be even: the two consumer groups take alternate tiles, and
+// with an even ring each stage (and its pair of mbarriers) belongs to one group
+// for ever, so that group observes every phase of its barriers in order.  With an
+// odd ring a group would revisit a stage only every second phase, and a parity
+// wait cannot tell phase n from phase n-2.
+constexpr int kStages = 6;
+static_assert(kStages % 2 == 0, "each stage must always be consumed by the same warp group");
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kDecodeThreads = kConsumerThreads + 32;
@@ -42,6 +48,8 @@ struct __align__(1024) DecodeSmem {
   int abort_flag;
 };
 
+static_assert(sizeof(DecodeSmem) + 1024 <= 227 * 1024, "shared memory budget of one CTA");
+
 struct DecodeParams {
   const __nv_bfloat16* q;
   int64_t q_stride;                 // elements between query tokens
@@ -53,6 +61,9 @@ struct DecodeParams {
   void* out;                        // (T, Hq, 128) bf16 or fp32
   float* lse_out;                   // (T, Hq) or null
   int32_t* status;
+#ifdef B200_TRACE
+  volatile int* trace;              // host-mapped progress records, 32 ints per CTA (debug builds)
+#endif
   int num_q_heads, num_kv_heads, group;
   int block_size, block_shift, num_blocks;
   int box_tokens, boxes_per_tile;
@@ -152,6 +163,14 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
         const int tok = (w.tile * kTileTokens + lane * p.box_tokens) & (p.block_size - 1);
         uint8_t* dst = sm.stage[s] + lane * p.box_tokens * 128;
         const int h = w.cur.kv_head;
+#ifdef B200_TRACE
+        if (p.trace && lane == 0) {
+          volatile int* tr = p.trace + blockIdx.x * 32;
+          tr[1] = h; tr[2] = tok; tr[3] = b; tr[4] = s; tr[5] = w.item; tr[6] = w.tile;
+          tr[0] = (int)it + 1;
+          __threadfence_system();
+        }
+#endif
         tma_load_4d(dst, &k_map, &sm.full[s], 0, h, tok, b);
         tma_load_4d(dst + kHalfTileBytes, &k_map, &sm.full[s], 64, h, tok, b);
         tma_load_4d(dst + kTileBytes, &v_map, &sm.full[s], 0, h, tok, b);
@@ -301,6 +320,12 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.empty[s]);
+#ifdef B200_TRACE
+      if (p.trace && lane == 0) {
+        p.trace[blockIdx.x * 32 + 8 + warp] = (int)it + 1;
+        __threadfence_system();
+      }
+#endif
     }
 
     // ---- merge the eight warps (fixed order) and write the item's result
@@ -459,6 +484,11 @@ decode_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ 
 
 }  // namespace b200
 
+#ifdef B200_TRACE
+static volatile int* g_trace = nullptr;
+extern "C" void b200_debug_set_trace(void* host_mapped) { g_trace = static_cast<volatile int*>(host_mapped); }
+#endif
+
 extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void* key_cache,
                                      const void* value_cache, int num_blocks, int block_size,
                                      const int32_t* block_table, int64_t bt_stride,
@@ -517,6 +547,9 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
   p.out = out;
   p.lse_out = lse_out;
   p.status = status;
+#ifdef B200_TRACE
+  p.trace = g_trace;
+#endif
   p.num_q_heads = num_q_heads;
   p.num_kv_heads = num_kv_heads;
   p.group = num_q_heads / num_kv_heads;
