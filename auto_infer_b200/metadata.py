@@ -1,0 +1,59 @@
+"""Per-step attention metadata.  The reference passes two host lists
+(cumulative query lengths, per-sequence kv lengths) to its vendor op on every
+layer (auto_infer/layers/attention/gqa.py:91-92).  Here they are turned into
+device-side work lists once per step and cached on the context object, so all
+layers of the step share one plan and one host-to-device copy."""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import ops
+
+_ATTR = "_b200_step_meta"
+
+
+class StepMetadata:
+    """Plans for one (step, head geometry): the split-KV decode plan covers the
+    sequences whose q_len * group fits one 16-row MMA tile; wider sequences
+    (prefill chunks) are listed for the prefill kernel."""
+
+    def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_q_heads: int,
+                 num_kv_heads: int, head_dim: int, device, causal_base: Optional[Sequence[int]] = None,
+                 num_ctas: Optional[int] = None):
+        self.cu_seqlens_q = [int(c) for c in cu_seqlens_q]
+        self.seqlens_kv = [int(k) for k in seqlens_kv]
+        if len(self.cu_seqlens_q) != len(self.seqlens_kv):
+            raise ValueError("cu_seqlens_q and seqlens_kv must have one entry per sequence")
+        self.num_tokens = self.cu_seqlens_q[-1] if self.cu_seqlens_q else 0
+        group = num_q_heads // num_kv_heads
+        prev = 0
+        self.prefill_seqs = []
+        for b, end in enumerate(self.cu_seqlens_q):
+            if (end - prev) * group > 16 and self.seqlens_kv[b] > 0:
+                self.prefill_seqs.append(b)
+            prev = end
+        self.decode = ops.DecodePlan(self.cu_seqlens_q, self.seqlens_kv, num_q_heads, num_kv_heads,
+                                     device, head_dim=head_dim, num_ctas=num_ctas,
+                                     causal_base=causal_base)
+        assert self.decode.skipped_seqs == len(self.prefill_seqs)
+
+
+def step_metadata(ctx, num_q_heads: int, num_kv_heads: int, head_dim: int, device,
+                  causal_base: Optional[Sequence[int]] = None) -> StepMetadata:
+    """Fetch (or build and attach) the metadata of ``ctx`` for this head
+    geometry.  The context is a plain mutable dataclass in the reference
+    (auto_infer/forward_context.py:9), which already carries per-step extras
+    such as the rope tables the same way (auto_infer/models/base.py:75)."""
+    cache = getattr(ctx, _ATTR, None)
+    if cache is None:
+        cache = {}
+        setattr(ctx, _ATTR, cache)
+    key = (num_q_heads, num_kv_heads, head_dim, str(device))
+    meta = cache.get(key)
+    if meta is None:
+        meta = StepMetadata(ctx.cu_seqlens_q, ctx.seqlens_kv, num_q_heads, num_kv_heads, head_dim,
+                            device, causal_base=causal_base)
+        cache[key] = meta
+    return meta
