@@ -89,7 +89,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu_index)],
+                 "-lms", "20", "-i", str(self.gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except Exception:
@@ -104,7 +104,7 @@ class ClockSampler:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
         self.proc.terminate()
-        sm, smax, reasons = [], [], set()
+        sm, smax, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
@@ -113,14 +113,17 @@ class ClockSampler:
             try:
                 sm.append(float(parts[1]))
                 smax.append(float(parts[2]))
+                power.append(float(parts[3]))
             except ValueError:
                 continue
             for name, val in zip(names, parts[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
+        load = [c for c, w in zip(sm, power) if w >= 0.5 * max(power)] if power else sm
+        return {"sm_mhz": statistics.median(load) if load else None,
                 "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "samples_under_load": len(load),
+                "power_w_max": max(power) if power else None, "reasons": sorted(reasons)}
 
 
 # --------------------------------------------------------------------------- #
@@ -283,9 +286,9 @@ def main():
     for _ in range(max(args.warmup, 3)):
         step()
     sampler = ClockSampler(local_rank)
-    barrier()
     if rank == 0:
         sampler.start()
+        time.sleep(0.3)                      # let the sampler come up before the timed region
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -294,7 +297,6 @@ def main():
     e1.record()
     barrier()
     elapsed_ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
     if world > 1:
         t = torch.tensor([elapsed_ms], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -362,6 +364,8 @@ def main():
         e2e_ms = float(t.item())
     e2e_value = total_kv_bytes / (e2e_ms * 1e-3) / 1e12
     status = ops.read_status(device)
+    # the sampler ran from before the timed region to the end of the end-to-end loop
+    clocks = sampler.stop() if rank == 0 else None
 
     # ---- smaller configurations and the CPU baseline (rank 0, N = 1) --------
     side, cpu = {}, None
