@@ -65,9 +65,9 @@ def measured_peak():
 
 def ncu_traffic(workload: str):
     """DRAM bytes per launch of the dominant kernel from the committed ncu
-    summary (profiles/roofline_traffic.json), or None."""
+    summary (profiles/roofline_traffic.txt), or None."""
     try:
-        with open(os.path.join(ROOT, "profiles", "roofline_traffic.json")) as fh:
+        with open(os.path.join(ROOT, "profiles", "roofline_traffic.txt")) as fh:
             return json.load(fh).get(workload)
     except Exception:
         return None
