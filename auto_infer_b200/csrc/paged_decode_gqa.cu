@@ -584,3 +584,61 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
   }
   return rc;
 }
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant.  Some hosts of this library may not allocate device
+// memory when a step runs: a serving engine that gave every free byte of HBM to
+// its paged KV pool at start-up has nothing left to allocate from, and a decode
+// loop that must keep its latency cannot afford the device-wide synchronisation
+// an allocation or a free implies.  For them the split-KV partial records live
+// in a fixed array that is part of the loaded module: it exists on every GPU
+// that loads the library, from load to exit, whether or not this entry point is
+// ever called.
+// ---------------------------------------------------------------------------
+namespace b200 {
+constexpr int kStaticMaxPartials = 1024;   // (o, lse) records; 8 256 B each -> 8.06 MiB in total
+constexpr size_t kStaticScratchFloats = (size_t)kStaticMaxPartials * (kMaxRows * kHeadDim + kMaxRows);
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+}  // namespace b200
+
+extern "C" int b200_paged_decode_gqa_static(const void* q, int64_t q_stride, const void* key_cache,
+                                            const void* value_cache, int num_blocks, int block_size,
+                                            const int32_t* block_table, int64_t bt_stride,
+                                            const int32_t* plan_dev,
+                                            const b200_decode_plan_info* info, int num_q_heads,
+                                            int num_kv_heads, int head_dim, float scale, void* out,
+                                            int out_is_f32, float* lse_out, int32_t* status,
+                                            void* stream) {
+  using namespace b200;
+  if (!info) {
+    set_last_error("paged_decode_gqa_static: plan info is null");
+    return B200_EINVAL;
+  }
+  if (info->num_partials > kStaticMaxPartials) {
+    set_last_error("paged_decode_gqa_static: the plan needs %d partial records but the built-in scratch "
+                   "holds %d; plan with fewer CTAs or use b200_paged_decode_gqa with a caller workspace",
+                   info->num_partials, kStaticMaxPartials);
+    return B200_ETOOLARGE;
+  }
+  // In host code the array's name is only a handle; the device address has to be
+  // asked for, once per device, with that device current.
+  static float* scratch_addr[64] = {nullptr};
+  int dev = 0;
+  int rc = check_cuda(cudaGetDevice(&dev), "paged_decode_gqa_static cudaGetDevice");
+  if (rc) return rc;
+  if (dev < 0 || dev >= 64) {
+    set_last_error("paged_decode_gqa_static: device ordinal %d outside the supported 0..63", dev);
+    return B200_EUNSUPPORTED;
+  }
+  if (scratch_addr[dev] == nullptr) {
+    float* addr = nullptr;
+    rc = check_cuda(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_decode_scratch),
+                    "paged_decode_gqa_static cudaGetSymbolAddress");
+    if (rc) return rc;
+    scratch_addr[dev] = addr;
+  }
+  return b200_paged_decode_gqa(q, q_stride, key_cache, value_cache, num_blocks, block_size, block_table,
+                               bt_stride, plan_dev, info, num_q_heads, num_kv_heads, head_dim, scale,
+                               scratch_addr[dev], kStaticScratchFloats * sizeof(float), out, out_is_f32,
+                               lse_out, status, stream);
+}

@@ -130,6 +130,39 @@ int b200_paged_decode_gqa(const void* q, int64_t q_stride,
                           int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Same attention as b200_paged_decode_gqa for callers that may not allocate
+ * device memory.  (No counterpart in the reference: its vendor op manages its
+ * own workspace.)  Two kinds of host are meant: a serving engine that handed
+ * all free HBM to the paged KV pool at start-up, so that an allocation made
+ * while a step runs can fail; and a latency-bound decode loop that cannot take
+ * the device-wide synchronisation an allocation or a free brings.  The split-KV
+ * partial records go to a fixed 8.06 MiB array inside the loaded module instead
+ * of a caller workspace; every GPU that loads the library carries that array
+ * until the process exits.  The call itself allocates nothing on the device
+ * and frees nothing.
+ *   - Limit: plans with more than 1024 partial records (info->num_partials;
+ *     at most num_ctas + num_seqs * Hkv) are refused with B200_ETOOLARGE and
+ *     nothing is launched.
+ *   - The first call on each device looks the array's device address up (and,
+ *     as any first launch does, loads the kernels); make that call during
+ *     start-up, with the device current, before any stream capture begins.
+ *   - All calls on a device share the one array and it keeps whatever the last
+ *     call left.  Nothing in it has to start at zero: every record is written
+ *     in full before it is read.  Two calls whose kernels overlap on the GPU
+ *     (different streams) race on it; keep such calls on one stream or order
+ *     them with events.
+ * All other arguments, outputs and return codes are those of
+ * b200_paged_decode_gqa. */
+int b200_paged_decode_gqa_static(const void* q, int64_t q_stride,
+                                 const void* key_cache, const void* value_cache,
+                                 int num_blocks, int block_size,
+                                 const int32_t* block_table, int64_t bt_stride,
+                                 const int32_t* plan_dev, const b200_decode_plan_info* info,
+                                 int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                 void* out, int out_is_f32, float* lse_out,
+                                 int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Merge n_parts normalised partial results by log-sum-exp:
  *   o_parts (n_parts, rows, D) fp32, lse_parts (n_parts, rows) fp32 (natural
  *   log, -inf = empty part)  ->  out (rows, D) bf16 (or fp32 if out_is_f32),
