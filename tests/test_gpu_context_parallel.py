@@ -1,0 +1,75 @@
+"""Context-parallel decode on GPUs.  On one GPU the R ranks are emulated one after
+the other (each with its own local block table and causal base) and their packed
+[o | lse] records merged by the CUDA merge kernel; with two or more GPUs the
+real NCCL path runs as child processes (NVLS off, plain all-gather)."""
+import os
+import sys
+
+import pytest
+import torch
+
+from oracle import paged_attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = dict(atol=2e-2, rtol=2e-2)
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.mark.parametrize("ranks", [2, 3, 8])
+def test_emulated_ranks_merge_to_the_unsplit_answer(ranks):
+    from auto_infer_b200 import context_parallel as cp, ops, synth
+    # MTP-verify rows (q_len 2) make the mask depend on global positions; the short
+    # sequence leaves trailing ranks without keys
+    b = synth.build_gqa_batch("cp", [(2, 1500), (1, 129), (2, 4096), (1, 2)], 32, 8, 128, 64, 17)
+    ref = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                              b.seqlens_kv, b.scale)
+    d = b.to("cuda")
+    rows = b.num_tokens * b.n_q
+    gathered = torch.empty(ranks, rows * (b.head_dim + 1), dtype=torch.float32, device="cuda")
+    for r in range(ranks):
+        local_kv, off, base = cp.shard_lengths(b.seqlens_kv, b.cu_seqlens_q, 128, r, ranks)
+        local_bt = cp.shard_block_table(d.block_table, b.seqlens_kv, 128, r, ranks)
+        plan = ops.DecodePlan(b.cu_seqlens_q, local_kv, b.n_q, b.n_kv, "cuda", causal_base=base)
+        buf = cp.PartialBuffer(b.num_tokens, b.n_q, b.head_dim, "cuda")
+        buf.clear()
+        ops.paged_decode_gqa(d.q, d.kv_cache[0], d.kv_cache[1], local_bt, plan, b.scale,
+                             out=buf.o, lse_out=buf.lse)
+        gathered[r].copy_(buf.flat)
+    o_parts, lse_parts = cp.split_gathered(gathered, rows, b.head_dim)
+    out = ops.lse_combine(o_parts, lse_parts)
+    torch.testing.assert_close(out.view_as(ref).cpu().float(), ref.float(), **TOL)
+    assert ops.read_status("cuda") == 0
+
+
+def _nccl_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    from auto_infer_b200 import context_parallel as cp, synth
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        b = synth.build_gqa_batch("cp", [(1, 3000), (2, 700), (1, 130)], 16, 8, 128, 40, 23)
+        d = b.to(f"cuda:{rank}")
+        local_bt = cp.shard_block_table(d.block_table, b.seqlens_kv, 128, rank, world)
+        step = cp.ContextParallelDecode(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, 128,
+                                        f"cuda:{rank}", cp_rank=rank, cp_size=world)
+        out = step.attend(d.q, d.kv_cache[0], d.kv_cache[1], local_bt, b.scale)
+        ref = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                                  b.seqlens_kv, b.scale)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL)
+        ret[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_gpu_nccl_all_gather_and_merge():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    port = 29600 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_nccl_worker, args=(2, port, ret), nprocs=2, join=True)
+        assert dict(ret) == {0: "ok", 1: "ok"}
