@@ -23,6 +23,11 @@ class DecodePlanInfo(ctypes.Structure):
         "total_tiles", "skipped_seqs", "plan_ints", "reserved")]
 
 
+class PrefillPlanInfo(ctypes.Structure):
+    """Mirror of ``b200_prefill_plan_info``."""
+    _fields_ = [(name, c_int32) for name in ("num_items", "total_tiles", "plan_ints", "reserved")]
+
+
 # name -> (restype, argtypes); one entry per function the header declares
 SIGNATURES = {
     "b200_version": (c_char_p, []),
@@ -43,6 +48,14 @@ SIGNATURES = {
     "b200_paged_decode_gqa_static": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, POINTER(DecodePlanInfo), c_int, c_int, c_int, c_float,
+        c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_prefill_plan_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "b200_prefill_plan": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+        c_void_p, c_size_t, POINTER(PrefillPlanInfo)]),
+    "b200_paged_prefill_gqa": (c_int, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+        c_void_p, POINTER(PrefillPlanInfo), c_int, c_int, c_int, c_float,
         c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_lse_combine": (c_int, [
         c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int,

@@ -20,6 +20,7 @@ SOURCES = [
     "decode_plan.cu",
     "reshape_and_cache.cu",
     "paged_decode_gqa.cu",
+    "paged_prefill_gqa.cu",
     "lse_combine.cu",
 ]
 

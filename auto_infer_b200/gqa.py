@@ -94,8 +94,9 @@ class B200GqaBackend(AttentionBackend):
         if meta.decode.info.num_items:
             ops.paged_decode_gqa(q, cache[0], cache[1], ctx.block_table, meta.decode, self.scale,
                                  out=out)
-        if meta.prefill_seqs:
-            ops.paged_prefill_gqa(q, cache[0], cache[1], ctx.block_table, meta, self.scale, out=out)
+        if meta.prefill is not None:
+            ops.paged_prefill_gqa(q, cache[0], cache[1], ctx.block_table, meta.prefill, self.scale,
+                                  out=out)
         return out
 
     def paged_attention(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,

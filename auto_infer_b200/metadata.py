@@ -38,6 +38,11 @@ class StepMetadata:
                                      device, head_dim=head_dim, num_ctas=num_ctas,
                                      causal_base=causal_base)
         assert self.decode.skipped_seqs == len(self.prefill_seqs)
+        self.prefill = None
+        if self.prefill_seqs:
+            self.prefill = ops.PrefillPlan(self.cu_seqlens_q, self.seqlens_kv, num_q_heads,
+                                           num_kv_heads, device, min_rows=16,
+                                           causal_base=causal_base)
 
 
 def step_metadata(ctx, num_q_heads: int, num_kv_heads: int, head_dim: int, device,

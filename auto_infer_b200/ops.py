@@ -9,7 +9,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from ._lib import DecodePlanInfo
+from ._lib import DecodePlanInfo, PrefillPlanInfo
 
 
 def _stream_ptr(device) -> int:
@@ -163,6 +163,73 @@ def paged_decode_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torc
             lse_out.data_ptr() if lse_out is not None else None,
             status_word(q.device).data_ptr(), _stream_ptr(q.device))
     _lib.check(rc, "b200_paged_decode_gqa")
+    return out
+
+
+class PrefillPlan:
+    """Host plan + device copy for the wide-query attention kernel: 128-row work
+    items of every (sequence, kv head) pair whose q_len * group exceeds
+    ``min_rows``, longest first."""
+
+    def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_q_heads: int,
+                 num_kv_heads: int, device, min_rows: int = 16,
+                 causal_base: Optional[Sequence[int]] = None):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("PrefillPlan needs a CUDA device (no CPU fallback)")
+        num_seqs = len(cu_seqlens_q)
+        num_tokens = int(cu_seqlens_q[-1]) if num_seqs else 0
+        nbytes = lib.b200_prefill_plan_bytes(num_seqs, num_tokens, num_q_heads, num_kv_heads)
+        self.host = torch.empty(max(nbytes // 4, 16), dtype=torch.int32, pin_memory=True)
+        cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
+        kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
+        base_ptr = None
+        if causal_base is not None:
+            base = torch.tensor(list(causal_base), dtype=torch.int32)
+            base_ptr = base.data_ptr()
+        self.info = PrefillPlanInfo()
+        rc = lib.b200_prefill_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, num_seqs, num_q_heads,
+                                   num_kv_heads, int(min_rows), self.host.data_ptr(),
+                                   self.host.numel() * 4, ctypes.byref(self.info))
+        _lib.check(rc, "b200_prefill_plan")
+        used = max(int(self.info.plan_ints), 16)
+        self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
+        self.dev.copy_(self.host[:used], non_blocking=True)
+
+
+def paged_prefill_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                      block_table: torch.Tensor, plan: PrefillPlan, scale: float,
+                      out: Optional[torch.Tensor] = None, out_f32: bool = False,
+                      lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged GQA attention for wide query blocks (chunked prefill, multi-token
+    verify); replaces ``paged_fia`` (auto_infer/layers/attention/base.py:48-61)
+    for the sequences in ``plan``.  Other rows of ``out`` are left untouched."""
+    _need_cuda(q, key_cache, value_cache, block_table)
+    lib = _lib.load()
+    t, n_q, d = q.shape
+    if q.stride(2) != 1 or q.stride(1) != d:
+        q = q.contiguous()
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("KV caches must be contiguous (num_blocks, block_size, Hkv, D)")
+    num_blocks, block_size, n_kv, _ = key_cache.shape
+    if block_table.dtype != torch.int32:
+        block_table = block_table.to(torch.int32)
+    if block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+    if out is None:
+        out = torch.empty(t, n_q, d, dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
+    elif not out.is_contiguous():
+        raise ValueError("out must be contiguous")
+    with torch.cuda.device(q.device):
+        rc = lib.b200_paged_prefill_gqa(
+            q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
+            num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+            plan.dev.data_ptr(), ctypes.byref(plan.info), n_q, n_kv, d, float(scale),
+            out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+            lse_out.data_ptr() if lse_out is not None else None,
+            status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "b200_paged_prefill_gqa")
     return out
 
 

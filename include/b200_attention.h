@@ -130,6 +130,41 @@ int b200_paged_decode_gqa(const void* q, int64_t q_stride,
                           int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Paged GQA attention for wide query blocks: chunked prefill over a cached
+ * prefix and multi-token verify, any q_len, bottom-right causal.  Replaces
+ * paged_fia (auto_infer/layers/attention/base.py:48-61) for the rows the decode
+ * kernel leaves out.  The host plan cuts every (sequence, kv head) pair into
+ * items of 128 packed query rows (row = query position x head within the kv
+ * group) and sorts them by decreasing key count.
+ *   min_rows: only sequences with q_len * (Hq/Hkv) > min_rows are planned
+ *             (16 complements b200_decode_plan; 0 plans every sequence).
+ * Arguments of the run call are those of b200_paged_decode_gqa without the
+ * workspace (this kernel needs none). */
+typedef struct b200_prefill_plan_info {
+  int32_t num_items;       /* 128-row work items                               */
+  int32_t total_tiles;     /* 64-token KV tiles summed over the items          */
+  int32_t plan_ints;       /* int32 words of the plan actually used            */
+  int32_t reserved;
+} b200_prefill_plan_info;
+
+size_t b200_prefill_plan_bytes(int num_seqs, int num_tokens, int num_q_heads, int num_kv_heads);
+
+int b200_prefill_plan(const int32_t* cu_seqlens_q_host, const int32_t* seqlens_kv_host,
+                      const int32_t* causal_base_host,
+                      int num_seqs, int num_q_heads, int num_kv_heads, int min_rows,
+                      int32_t* plan_host, size_t plan_bytes,
+                      b200_prefill_plan_info* info);
+
+int b200_paged_prefill_gqa(const void* q, int64_t q_stride,
+                           const void* key_cache, const void* value_cache,
+                           int num_blocks, int block_size,
+                           const int32_t* block_table, int64_t bt_stride,
+                           const int32_t* plan_dev, const b200_prefill_plan_info* info,
+                           int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                           void* out, int out_is_f32, float* lse_out,
+                           int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Same attention as b200_paged_decode_gqa for callers that may not allocate
  * device memory.  (No counterpart in the reference: its vendor op manages its
  * own workspace.)  Two kinds of host are meant: a serving engine that handed

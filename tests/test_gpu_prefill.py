@@ -1,0 +1,89 @@
+"""Parity of the wide-query (chunked prefill / multi-token verify) attention
+kernel with the oracle and the reference's golden outputs, through the C ABI.
+Tolerance for bf16 outputs: rtol 2e-2 / atol 2e-2."""
+import pytest
+import torch
+
+from oracle import paged_attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+TOL = dict(atol=2e-2, rtol=2e-2)
+
+
+def _prefill(q, kc, vc, bt, cu, kv, scale, n_q, n_kv, min_rows=0, want_lse=False):
+    from auto_infer_b200 import ops
+    plan = ops.PrefillPlan(cu, kv, n_q, n_kv, "cuda", min_rows=min_rows)
+    lse = torch.empty(q.shape[0], n_q, dtype=torch.float32, device="cuda") if want_lse else None
+    out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
+    ops.paged_prefill_gqa(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), plan, scale, out=out, lse_out=lse)
+    torch.cuda.synchronize()
+    assert ops.read_status("cuda") == 0
+    return (out.cpu(), lse.cpu()) if want_lse else out.cpu()
+
+
+@pytest.mark.parametrize("name", ["chunk_prefill_bs128", "decode_bs16", "mtp_verify_bs128",
+                                  "drafter_ragged_bs16"])
+def test_golden_reference_outputs(golden_paged, name):
+    """Every golden case, decode-shaped ones included: the kernel handles any q_len."""
+    case = next(c for c in golden_paged["paged"] if c["name"] == name)
+    out = _prefill(case["q"], case["k_cache"], case["v_cache"], case["block_table"], case["cu"],
+                   case["kv_lens"], case["scale"], case["n_q"], case["n_kv"])
+    torch.testing.assert_close(out.float(), case["out"].float(), **TOL)
+
+
+@pytest.mark.parametrize("q_len,prefix", [(1, 0), (33, 0), (128, 0), (129, 64), (200, 1000), (512, 300)])
+def test_chunk_over_prefix_shapes(q_len, prefix):
+    from auto_infer_b200 import synth
+    b = synth.build_gqa_batch("chunk", [(q_len, prefix + q_len), (7, 77)], 8, 2, 128, 24, 300 + q_len)
+    ref, ref_lse = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table,
+                                       b.cu_seqlens_q, b.seqlens_kv, b.scale, return_lse=True)
+    out, lse = _prefill(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                        b.seqlens_kv, b.scale, b.n_q, b.n_kv, want_lse=True)
+    torch.testing.assert_close(out.float(), ref.float(), **TOL)
+    torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
+
+
+def test_mixed_batch_through_the_backend():
+    """Decode rows and prefill chunks in one step, as the scheduler orders them
+    (decode first): the backend sends each row to the kernel built for it and the
+    slot write comes first."""
+    from auto_infer_b200 import ops, synth
+    from auto_infer_b200.forward_context import ForwardContext
+    from auto_infer_b200.gqa import B200GqaBackend
+    seqs = [(1, 700), (1, 64), (2, 333), (96, 96 + 256), (40, 40)]
+    b = synth.build_gqa_batch("mixed", seqs, 16, 4, 128, 32, 55, shared_prefix_tokens=[0, 0, 0, 256, 0])
+    d = b.to("cuda")
+    backend = B200GqaBackend(b.n_q, b.n_kv, b.head_dim, b.scale, 1, "cuda", torch.bfloat16)
+    ctx = ForwardContext(None, None, d.slot_mapping, d.block_table, b.cu_seqlens_q, b.seqlens_kv,
+                         None, backend, [d.kv_cache], False)
+    out = backend.paged_attention(0, d.q, d.k_new, d.v_new, ctx)
+    orc.write_kv(b.k_new, b.v_new, b.kv_cache[0], b.kv_cache[1], b.slot_mapping.tolist())
+    assert torch.equal(d.kv_cache.cpu(), b.kv_cache)
+    ref = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                              b.seqlens_kv, b.scale)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL)
+    assert ops.read_status("cuda") == 0
+
+
+def test_config2_full_size_mixed_batch():
+    """Config 2: 60 decode rows + four 512-token chunks over nested shared
+    prefixes of 0/1024/2048/4096 tokens (aliased physical blocks)."""
+    from auto_infer_b200 import ops, synth
+    from auto_infer_b200.forward_context import ForwardContext
+    from auto_infer_b200.gqa import B200GqaBackend
+    d = synth.config2("cuda")            # 2 GiB pool: generated on the device, copied back for the oracle
+    b = d.to("cpu")
+    assert b.block_table[61, 0] == b.block_table[62, 0] == b.block_table[63, 0]
+    backend = B200GqaBackend(b.n_q, b.n_kv, b.head_dim, b.scale, 1, "cuda", torch.bfloat16)
+    ctx = ForwardContext(None, None, d.slot_mapping, d.block_table, b.cu_seqlens_q, b.seqlens_kv,
+                         None, backend, [d.kv_cache], False)
+    out = backend.paged_attention(0, d.q, d.k_new, d.v_new, ctx).cpu()
+    # shared prefix blocks are written by several requests in this synthetic step only where
+    # their new tokens land, which is never inside the shared (full, read-only) blocks
+    orc.write_kv(b.k_new, b.v_new, b.kv_cache[0], b.kv_cache[1], b.slot_mapping.tolist())
+    assert torch.equal(d.kv_cache.cpu(), b.kv_cache)
+    torch.set_num_threads(max(torch.get_num_threads(), 8))
+    ref = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                              b.seqlens_kv, b.scale, literal_max_kv=0)
+    torch.testing.assert_close(out.float(), ref.float(), **TOL)
+    assert ops.read_status("cuda") == 0
