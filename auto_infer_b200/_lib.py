@@ -57,6 +57,14 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, POINTER(PrefillPlanInfo), c_int, c_int, c_int, c_float,
         c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_mla_decode_plan": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+        c_void_p, c_size_t, POINTER(DecodePlanInfo)]),
+    "b200_mla_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "b200_mla_decode_absorbed": (c_int, [
+        c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64,
+        c_void_p, POINTER(DecodePlanInfo), c_int, c_int, c_int, c_float,
+        c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_lse_combine": (c_int, [
         c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int,
         c_void_p, c_int, c_void_p, c_void_p]),

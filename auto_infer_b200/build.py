@@ -21,6 +21,7 @@ SOURCES = [
     "reshape_and_cache.cu",
     "paged_decode_gqa.cu",
     "paged_prefill_gqa.cu",
+    "mla_decode.cu",
     "lse_combine.cu",
 ]
 

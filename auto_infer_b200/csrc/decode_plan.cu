@@ -25,17 +25,45 @@ extern "C" size_t b200_decode_workspace_bytes(int num_seqs, int num_kv_heads, in
   return parts * (kMaxRows * (size_t)head_dim + kMaxRows) * sizeof(float) + 256;
 }
 
+static int build_split_plan(const char* who, int tile_tokens, const int32_t* cu_q,
+                            const int32_t* kv_lens, const int32_t* causal_base, int num_seqs,
+                            int num_q_heads, int num_kv_heads, int num_ctas, int32_t* plan,
+                            size_t plan_bytes, b200_decode_plan_info* info);
+
 extern "C" int b200_decode_plan(const int32_t* cu_q, const int32_t* kv_lens,
                                 const int32_t* causal_base, int num_seqs, int num_q_heads,
                                 int num_kv_heads, int num_ctas, int32_t* plan, size_t plan_bytes,
                                 b200_decode_plan_info* info) {
+  return build_split_plan("decode_plan", kTileTokens, cu_q, kv_lens, causal_base, num_seqs,
+                          num_q_heads, num_kv_heads, num_ctas, plan, plan_bytes, info);
+}
+
+// The latent (MLA) decode kernel streams 32-token tiles of one shared latent head.
+extern "C" int b200_mla_decode_plan(const int32_t* cu_q, const int32_t* kv_lens,
+                                    const int32_t* causal_base, int num_seqs, int num_heads,
+                                    int num_ctas, int32_t* plan, size_t plan_bytes,
+                                    b200_decode_plan_info* info) {
+  return build_split_plan("mla_decode_plan", kMlaTileTokens, cu_q, kv_lens, causal_base, num_seqs,
+                          num_heads, 1, num_ctas, plan, plan_bytes, info);
+}
+
+extern "C" size_t b200_mla_decode_workspace_bytes(int num_seqs, int num_ctas, int kv_lora_rank) {
+  if (num_seqs < 0 || num_ctas <= 0 || kv_lora_rank <= 0) return 0;
+  const size_t parts = (size_t)num_ctas + (size_t)num_seqs;
+  return parts * (kMaxRows * (size_t)kv_lora_rank + kMaxRows) * sizeof(float) + 256;
+}
+
+static int build_split_plan(const char* who, int tile_tokens, const int32_t* cu_q,
+                            const int32_t* kv_lens, const int32_t* causal_base, int num_seqs,
+                            int num_q_heads, int num_kv_heads, int num_ctas, int32_t* plan,
+                            size_t plan_bytes, b200_decode_plan_info* info) {
   if (!plan || !info || num_seqs < 0 || (num_seqs > 0 && (!cu_q || !kv_lens)) || num_q_heads <= 0 ||
       num_kv_heads <= 0 || num_ctas <= 0 || num_q_heads % num_kv_heads != 0) {
-    set_last_error("decode_plan: bad argument (null pointer, heads not divisible, or size <= 0)");
+    set_last_error("%s: bad argument (null pointer, heads not divisible, or size <= 0)", who);
     return B200_EINVAL;
   }
   if (plan_bytes < b200_decode_plan_bytes(num_seqs, num_kv_heads, num_ctas)) {
-    set_last_error("decode_plan: plan buffer of %zu bytes is smaller than b200_decode_plan_bytes()",
+    set_last_error("%s: plan buffer of %zu bytes is smaller than b200_decode_plan_bytes()", who,
                    plan_bytes);
     return B200_EPLAN;
   }
@@ -50,7 +78,7 @@ extern "C" int b200_decode_plan(const int32_t* cu_q, const int32_t* kv_lens,
     const int q_len = cu_q[b] - prev;
     prev = cu_q[b];
     if (q_len < 0 || kv_lens[b] < 0) {
-      set_last_error("decode_plan: sequence %d has negative length", b);
+      set_last_error("%s: sequence %d has negative length", who, b);
       return B200_EINVAL;
     }
     if (q_len == 0 || kv_lens[b] == 0) continue;
@@ -58,10 +86,10 @@ extern "C" int b200_decode_plan(const int32_t* cu_q, const int32_t* kv_lens,
       ++skipped;
       continue;
     }
-    total += (int64_t)((kv_lens[b] + kTileTokens - 1) / kTileTokens) * num_kv_heads;
+    total += (int64_t)((kv_lens[b] + tile_tokens - 1) / tile_tokens) * num_kv_heads;
   }
   if (total > INT32_MAX) {
-    set_last_error("decode_plan: %lld tiles exceed the int32 plan format", (long long)total);
+    set_last_error("%s: %lld tiles exceed the int32 plan format", who, (long long)total);
     return B200_ETOOLARGE;
   }
 
@@ -88,7 +116,7 @@ extern "C" int b200_decode_plan(const int32_t* cu_q, const int32_t* kv_lens,
     const int q_len = cu_q[b] - prev;
     prev = cu_q[b];
     if (q_len == 0 || kv_lens[b] == 0 || q_len * group > kMaxRows) continue;
-    const int tiles = (kv_lens[b] + kTileTokens - 1) / kTileTokens;
+    const int tiles = (kv_lens[b] + tile_tokens - 1) / tile_tokens;
     const int base = causal_base ? causal_base[b] : kv_lens[b] - q_len;
     for (int h = 0; h < num_kv_heads; ++h) {
       int t = 0;

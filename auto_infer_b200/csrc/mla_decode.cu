@@ -1,0 +1,544 @@
+// Absorbed-MLA decode attention for sm_100a: all heads attend one shared latent
+// "kv head" of width kv_lora_rank + rope (512 + 64), stored ONCE per token; the
+// same shared-memory tile serves as K (576 wide) and as V (its first 512 dims).
+//
+// HBM-bound at 16 heads (34 816 flop per 1 152-byte latent row = 30 flop/B), so
+// the design is the split-KV streaming design of the GQA decode kernel:
+//   * host plan: 32-token latent tiles of all sequences laid end to end and cut
+//     into one equal range per CTA (persistent CTA per SM);
+//   * producer warp: nine 4 KB TMA boxes (64 dims x 32 tokens, 128-byte swizzle)
+//     per tile into a 4-stage ring (36 KB per stage);
+//   * two consumer groups of four warps take alternate tiles (even ring: a stage
+//     always belongs to one group).  Inside a group, warps 0-1 compute
+//     S = Q K^T for 16 tokens each over all 576 dims (q_len*heads <= 16 rows form
+//     the M of mma.sync m16n8k16; Q fragments come from shared memory), the
+//     group agrees on the row maxima through shared memory, P goes to shared
+//     memory as bf16, and all four warps accumulate O += P V for 128 of the 512
+//     value dims each;
+//   * the groups' (m, l, O) are merged in a fixed order at the end of an item.
+// Algorithmic bytes per launch: sum_b kv_len_b * 1 152 B (+ q, o).
+#include "common.cuh"
+#include "decode_plan.h"
+
+namespace b200 {
+
+constexpr int kLatentDim = 576;
+constexpr int kValueDim = 512;
+constexpr int kMlaSub = kLatentDim / 64;                      // 64-dim sub-tiles per latent row
+constexpr int kMlaSubBytes = kMlaTileTokens * 128;            // [32 tokens][64 dims] bf16
+constexpr int kMlaStageBytes = kMlaSub * kMlaSubBytes;        // 36 864
+constexpr int kMlaStages = 4;
+static_assert(kMlaStages % 2 == 0, "each stage must always be consumed by the same warp group");
+constexpr int kMlaWarps = 8;
+constexpr int kMlaConsumerThreads = kMlaWarps * 32;
+constexpr int kMlaThreads = kMlaConsumerThreads + 32;
+constexpr int kQPitch = kLatentDim * 2 + 16;                  // bytes per Q row in shared memory
+constexpr int kPPitch = kMlaTileTokens * 2 + 16;              // bytes per P row in shared memory
+
+struct __align__(1024) MlaSmem {
+  uint8_t stage[kMlaStages][kMlaStageBytes];
+  float slots[4][kMaxRows * 128];                             // merge buffer: one 128-dim slice per warp pair
+  __align__(16) uint8_t qbuf[kMaxRows * kQPitch];
+  __align__(16) uint8_t pbuf[2][kMaxRows * kPPitch];
+  float m_part[2][2][kMaxRows];
+  float red_m[2][kMaxRows];
+  float red_l[kMlaWarps][kMaxRows];
+  uint64_t full[kMlaStages];
+  uint64_t empty[kMlaStages];
+  int abort_flag;
+};
+static_assert(sizeof(MlaSmem) + 1024 <= 227 * 1024, "shared memory budget of one CTA");
+
+struct MlaParams {
+  const __nv_bfloat16* q;          // (T, H, 576)
+  int64_t q_stride;
+  const int32_t* block_table;
+  int64_t bt_stride;
+  const int32_t* plan;
+  float* part_o;                   // (num_partials, 16, 512)
+  float* part_lse;                 // (num_partials, 16)
+  void* out;                       // (T, H, 512) bf16 or fp32
+  float* lse_out;
+  int32_t* status;
+  int num_heads;
+  int block_size, block_shift, num_blocks, box_tokens, boxes_per_tile;
+  int out_is_f32;
+  float scale, scale_log2;
+};
+
+struct MlaWalker {
+  const DecodeItem* items;
+  int item, item_end, tile, tile_end;
+  DecodeItem cur;
+  __device__ __forceinline__ void load() {
+    if (item < item_end) {
+      const int4* p = reinterpret_cast<const int4*>(items + item);
+      int4 a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2);
+      cur.seq = a.x; cur.kv_head = a.y; cur.tile_begin = a.z; cur.tile_end = a.w;
+      cur.kv_len = b.x; cur.q_start = b.y; cur.q_len = b.z; cur.causal_base = b.w;
+      cur.partial_idx = c.x; cur.direct = c.y;
+      tile = cur.tile_begin;
+      tile_end = cur.tile_end;
+    }
+  }
+};
+
+__global__ void __launch_bounds__(kMlaThreads, 1)
+mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  MlaSmem& sm = *reinterpret_cast<MlaSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int32_t* plan = p.plan;
+  const int32_t* cta_off = plan + plan[kHdrOffCta];
+  const DecodeItem* items = reinterpret_cast<const DecodeItem*>(plan + plan[kHdrOffItems]);
+  const int item_begin = cta_off[blockIdx.x];
+  const int item_end = cta_off[blockIdx.x + 1];
+
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    for (int s = 0; s < kMlaStages; ++s) {
+      mbar_init(&sm.full[s], 1);
+      mbar_init(&sm.empty[s], 4);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (item_begin >= item_end) return;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (warp == kMlaWarps) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0) tma_prefetch_desc(&lat_map);
+    MlaWalker w{items, item_begin, item_end, 0, 0, {}};
+    w.load();
+    uint32_t it = 0;
+    const int nbox = p.boxes_per_tile;
+    auto fetch_block = [&](const MlaWalker& tw) -> int {
+      if (lane >= nbox) return 0;
+      const int last_block = (tw.cur.kv_len - 1) >> p.block_shift;
+      int lb = ((tw.tile * kMlaTileTokens) >> p.block_shift) + lane;
+      lb = lb > last_block ? last_block : lb;
+      return __ldg(p.block_table + (int64_t)tw.cur.seq * p.bt_stride + lb);
+    };
+    int bid = fetch_block(w);
+    while (w.item < w.item_end) {
+      MlaWalker nxt = w;
+      ++nxt.tile;
+      if (nxt.tile >= nxt.tile_end) {
+        ++nxt.item;
+        nxt.load();
+      }
+      int bid_next = 0;
+      if (nxt.item < nxt.item_end) bid_next = fetch_block(nxt);
+      const int s = it % kMlaStages;
+      if (lane == 0) {
+        mbar_wait_bounded(&sm.empty[s], ((it / kMlaStages) & 1u) ^ 1u, abort_flag, p.status);
+        mbar_arrive_expect_tx(&sm.full[s], kMlaStageBytes);
+      }
+      __syncwarp();
+      // box i of the tile by lane i; each lane issues its nine 64-dim slices
+      if (lane < nbox) {
+        int b = bid;
+        if (b < 0 || b >= p.num_blocks) {
+          if (p.status) atomicOr(p.status, B200_STATUS_BAD_BLOCK);
+          b = p.num_blocks;
+        }
+        const int tok = (w.tile * kMlaTileTokens + lane * p.box_tokens) & (p.block_size - 1);
+        uint8_t* dst = sm.stage[s] + lane * p.box_tokens * 128;
+#pragma unroll
+        for (int c = 0; c < kMlaSub; ++c)
+          tma_load_4d(dst + c * kMlaSubBytes, &lat_map, &sm.full[s], c * 64, 0, tok, b);
+      }
+      __syncwarp();
+      ++it;
+      w = nxt;
+      bid = bid_next;
+    }
+    if (lane == 0) {
+      const uint32_t n = it < (uint32_t)kMlaStages ? it : (uint32_t)kMlaStages;
+      for (uint32_t k = 0; k < n; ++k) {
+        const uint32_t j = it - 1 - k;
+        mbar_wait_bounded(&sm.full[j % kMlaStages], (j / kMlaStages) & 1u, abort_flag, p.status);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  const int grp = warp >> 2;
+  const int gw = warp & 3;             // warp within the group: S slice (0,1) and value-dim slice (0..3)
+  const int quad = lane >> 2;
+  const int qlane = lane & 3;
+  const int G = p.num_heads;
+  const int gbar = 1 + grp;            // named barrier of the group (128 threads)
+
+  // ldmatrix lane addressing
+  const int k_tok = gw * 16 + ((lane >> 4) << 3) + (lane & 7);        // K operand (S warps only)
+  const int k_chunk_sel = (lane >> 3) & 1;
+  const int v_tok_l = (((lane >> 3) & 1) << 3) + (lane & 7);          // V operand
+  const int v_chunk_sel = lane >> 4;
+  // A operands from row-major shared memory: matrices (r0-7,k0-7) (r8-15,k0-7) (r0-7,k8-15) (r8-15,k8-15)
+  const int a_row = (lane & 7) + (((lane >> 3) & 1) << 3);
+  const int a_koff = (lane >> 4) << 3;
+
+  MlaWalker w{items, item_begin, item_end, 0, 0, {}};
+  w.load();
+  uint32_t it = 0;
+
+  while (w.item < w.item_end) {
+    const DecodeItem item = w.cur;
+    const int rows = item.q_len * G;
+    // ---- stage Q (rows x 576, zero padded to 16 rows) in shared memory
+    for (int i = threadIdx.x; i < kMaxRows * (kLatentDim / 8); i += kMlaConsumerThreads) {
+      const int r = i / (kLatentDim / 8), c = i % (kLatentDim / 8);
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (r < rows) {
+        const __nv_bfloat16* src = p.q + (int64_t)(item.q_start + r / G) * p.q_stride +
+                                   (int64_t)(r % G) * kLatentDim + c * 8;
+        v = __ldg(reinterpret_cast<const uint4*>(src));
+      }
+      *reinterpret_cast<uint4*>(sm.qbuf + r * kQPitch + c * 16) = v;
+    }
+    named_bar_sync(3, kMlaConsumerThreads);
+
+    const int lim0 = quad < rows ? min(item.causal_base + quad / G, item.kv_len - 1) : -1;
+    const int lim1 = quad + 8 < rows ? min(item.causal_base + (quad + 8) / G, item.kv_len - 1) : -1;
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    const uint32_t qbase = smem_u32(sm.qbuf) + a_row * kQPitch + a_koff * 2;
+    const uint32_t pbase = smem_u32(sm.pbuf[grp]) + a_row * kPPitch + a_koff * 2;
+
+    for (int tile = item.tile_begin; tile < item.tile_end; ++tile, ++it) {
+      if ((int)(it & 1u) != grp) continue;
+      const int s = it % kMlaStages;
+      mbar_wait_bounded(&sm.full[s], (it / kMlaStages) & 1u, abort_flag, p.status);
+      const uint32_t sbase = smem_u32(sm.stage[s]);
+
+      float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      if (gw < 2) {
+        // ---- S = Q K^T for this warp's 16 tokens over 576 dims
+#pragma unroll 4
+        for (int ks = 0; ks < kLatentDim / 16; ++ks) {
+          uint32_t qa[4], kb[4];
+          ldmatrix_x4(qa, qbase + ks * 32);
+          const int chunk = (ks & 3) * 2 + k_chunk_sel;
+          ldmatrix_x4(kb, sbase + (ks >> 2) * kMlaSubBytes + swz128(k_tok, chunk));
+          mma_bf16_16816(sacc[0], qa, kb[0], kb[1]);
+          mma_bf16_16816(sacc[1], qa, kb[2], kb[3]);
+        }
+        const int tok0 = tile * kMlaTileTokens + gw * 16 + qlane * 2;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = tok0 + n * 8 + e;
+            if (j > lim0) sacc[n][e] = -INFINITY;
+            if (j > lim1) sacc[n][2 + e] = -INFINITY;
+            mx0 = fmaxf(mx0, sacc[n][e]);
+            mx1 = fmaxf(mx1, sacc[n][2 + e]);
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if (qlane == 0) {
+          sm.m_part[grp][gw][quad] = mx0;
+          sm.m_part[grp][gw][quad + 8] = mx1;
+        }
+      }
+      named_bar_sync(gbar, 128);
+      // ---- group-wide row maxima, correction of the running state
+      const float mn0 = fmaxf(m0, fmaxf(sm.m_part[grp][0][quad], sm.m_part[grp][1][quad]));
+      const float mn1 = fmaxf(m1, fmaxf(sm.m_part[grp][0][quad + 8], sm.m_part[grp][1][quad + 8]));
+      const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0 * p.scale_log2;
+      const float ms1 = (mn1 == -INFINITY) ? 0.f : mn1 * p.scale_log2;
+      if (__any_sync(0xffffffffu, (mn0 != m0) || (mn1 != m1))) {
+        const float c0 = fast_exp2(m0 * p.scale_log2 - ms0);
+        const float c1 = fast_exp2(m1 * p.scale_log2 - ms1);
+        l0 *= c0;
+        l1 *= c1;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
+        }
+        m0 = mn0;
+        m1 = mn1;
+      }
+      if (gw < 2) {
+        // ---- P (bf16) to shared memory, row-major [16][32 tokens]
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          const float p0 = fast_exp2(fmaf(sacc[n][0], p.scale_log2, -ms0));
+          const float p1 = fast_exp2(fmaf(sacc[n][1], p.scale_log2, -ms0));
+          const float p2 = fast_exp2(fmaf(sacc[n][2], p.scale_log2, -ms1));
+          const float p3 = fast_exp2(fmaf(sacc[n][3], p.scale_log2, -ms1));
+          l0 += p0 + p1;
+          l1 += p2 + p3;
+          const int col = gw * 16 + n * 8 + qlane * 2;
+          *reinterpret_cast<uint32_t*>(sm.pbuf[grp] + quad * kPPitch + col * 2) = pack_bf16(p0, p1);
+          *reinterpret_cast<uint32_t*>(sm.pbuf[grp] + (quad + 8) * kPPitch + col * 2) = pack_bf16(p2, p3);
+        }
+      }
+      named_bar_sync(gbar, 128);
+      // ---- O[:, 128*gw .. +128) += P V over the tile's 32 tokens
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        uint32_t pa[4];
+        ldmatrix_x4(pa, pbase + kt * 32);
+        const int tok = kt * 16 + v_tok_l;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int chunk = (j & 3) * 2 + v_chunk_sel;
+          const int sub = gw * 2 + (j >> 2);
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, sbase + sub * kMlaSubBytes + swz128(tok, chunk));
+          mma_bf16_16816(o[2 * j], pa, vb[0], vb[1]);
+          mma_bf16_16816(o[2 * j + 1], pa, vb[2], vb[3]);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.empty[s]);
+    }
+
+    // ---- merge the two groups in a fixed order, write the item's result
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (qlane == 0) {
+      if (gw == 0) {
+        sm.red_m[grp][quad] = m0;
+        sm.red_m[grp][quad + 8] = m1;
+      }
+      sm.red_l[warp][quad] = l0;           // zero for the warps that computed no S
+      sm.red_l[warp][quad + 8] = l1;
+    }
+    named_bar_sync(3, kMlaConsumerThreads);
+    const float ga0 = fmaxf(sm.red_m[0][quad], sm.red_m[1][quad]);
+    const float ga1 = fmaxf(sm.red_m[0][quad + 8], sm.red_m[1][quad + 8]);
+    {
+      const float f0 = (m0 == -INFINITY) ? 0.f : fast_exp2((m0 - ga0) * p.scale_log2);
+      const float f1 = (m1 == -INFINITY) ? 0.f : fast_exp2((m1 - ga1) * p.scale_log2);
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        o[n][0] *= f0; o[n][1] *= f0; o[n][2] *= f1; o[n][3] *= f1;
+      }
+    }
+    if (grp == 1) {
+      float* slot = sm.slots[gw];
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        const int col = n * 8 + qlane * 2;
+        *reinterpret_cast<float2*>(slot + quad * 128 + col) = make_float2(o[n][0], o[n][1]);
+        *reinterpret_cast<float2*>(slot + (quad + 8) * 128 + col) = make_float2(o[n][2], o[n][3]);
+      }
+    }
+    named_bar_sync(3, kMlaConsumerThreads);
+    if (grp == 0) {
+      const float* slot = sm.slots[gw];
+      // row sums over both groups
+      float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+      for (int g2 = 0; g2 < 2; ++g2) {
+        const float mg0 = sm.red_m[g2][quad], mg1 = sm.red_m[g2][quad + 8];
+        const float s0 = (mg0 == -INFINITY) ? 0.f : fast_exp2((mg0 - ga0) * p.scale_log2);
+        const float s1 = (mg1 == -INFINITY) ? 0.f : fast_exp2((mg1 - ga1) * p.scale_log2);
+#pragma unroll
+        for (int ww = 0; ww < 4; ++ww) {
+          ls0 += sm.red_l[g2 * 4 + ww][quad] * s0;
+          ls1 += sm.red_l[g2 * 4 + ww][quad + 8] * s1;
+        }
+      }
+      const float inv0 = ls0 > 0.f ? 1.f / ls0 : 0.f;
+      const float inv1 = ls1 > 0.f ? 1.f / ls1 : 0.f;
+      const float lse0 = ls0 > 0.f ? ga0 * p.scale + __logf(ls0) : -INFINITY;
+      const float lse1 = ls1 > 0.f ? ga1 * p.scale + __logf(ls1) : -INFINITY;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = quad + half * 8;
+        if (row >= rows) continue;
+        const float inv = half ? inv1 : inv0;
+        const int64_t tok = item.q_start + row / G;
+        const int head = row % G;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          const int col = n * 8 + qlane * 2;
+          const float2 other = *reinterpret_cast<const float2*>(slot + row * 128 + col);
+          const float x = (o[n][half * 2] + other.x) * inv;
+          const float y = (o[n][half * 2 + 1] + other.y) * inv;
+          const int vcol = gw * 128 + col;
+          if (item.direct) {
+            const int64_t off = (tok * p.num_heads + head) * kValueDim + vcol;
+            if (p.out_is_f32)
+              *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + off) = make_float2(x, y);
+            else
+              *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pack_bf16(x, y);
+          } else {
+            float* dst = p.part_o + ((int64_t)item.partial_idx * kMaxRows + row) * kValueDim + vcol;
+            *reinterpret_cast<float2*>(dst) = make_float2(x, y);
+          }
+        }
+        if (gw == 0 && qlane == 0) {
+          const float lse = half ? lse1 : lse0;
+          if (item.direct) {
+            if (p.lse_out) p.lse_out[tok * p.num_heads + head] = lse;
+          } else {
+            p.part_lse[(int64_t)item.partial_idx * kMaxRows + row] = lse;
+          }
+        }
+      }
+    }
+    // the Q staging of the next item waits on barrier 3 again; nobody can still be
+    // reading qbuf / slots of this item by then (all reads precede a barrier above
+    // or belong to warps that must reach the next barrier themselves)
+    named_bar_sync(3, kMlaConsumerThreads);
+    ++w.item;
+    w.load();
+  }
+}
+
+// Merge of the partial (o, lse) records of sequences cut across CTAs: one CTA
+// of 256 threads per sequence, thread -> (row, 32 value columns).
+__global__ void __launch_bounds__(256)
+mla_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ part_o,
+                 const float* __restrict__ part_lse, void* __restrict__ out,
+                 float* __restrict__ lse_out, int num_heads, int out_is_f32) {
+  const MultiGroup g = reinterpret_cast<const MultiGroup*>(plan + plan[kHdrOffMulti])[blockIdx.x];
+  const int rows = g.q_len * num_heads;
+  const int row = threadIdx.x >> 4;
+  const int col0 = (threadIdx.x & 15) * 32;
+  if (row >= rows) return;
+  float mx = -INFINITY;
+  for (int pidx = g.part_begin; pidx < g.part_end; ++pidx)
+    mx = fmaxf(mx, part_lse[(int64_t)pidx * kMaxRows + row]);
+  float wsum = 0.f;
+  for (int pidx = g.part_begin; pidx < g.part_end; ++pidx) {
+    const float l = part_lse[(int64_t)pidx * kMaxRows + row];
+    wsum += (l == -INFINITY) ? 0.f : __expf(l - mx);
+  }
+  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+  const int64_t tok = g.q_start + row / num_heads;
+  const int head = row % num_heads;
+  for (int c = 0; c < 32; c += 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int pidx = g.part_begin; pidx < g.part_end; ++pidx) {
+      const float l = part_lse[(int64_t)pidx * kMaxRows + row];
+      const float wgt = (l == -INFINITY) ? 0.f : __expf(l - mx) * inv;
+      const float4 x = *reinterpret_cast<const float4*>(
+          part_o + ((int64_t)pidx * kMaxRows + row) * kValueDim + col0 + c);
+      acc.x += wgt * x.x; acc.y += wgt * x.y; acc.z += wgt * x.z; acc.w += wgt * x.w;
+    }
+    const int64_t off = (tok * num_heads + head) * kValueDim + col0 + c;
+    if (out_is_f32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + off) = acc;
+    } else {
+      uint2 pk;
+      pk.x = pack_bf16(acc.x, acc.y);
+      pk.y = pack_bf16(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + off) = pk;
+    }
+  }
+  if (lse_out && (threadIdx.x & 15) == 0)
+    lse_out[tok * num_heads + head] = wsum > 0.f ? mx + __logf(wsum) : -INFINITY;
+}
+
+}  // namespace b200
+
+extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
+                                        const void* latent_cache, int num_blocks, int block_size,
+                                        const int32_t* block_table, int64_t bt_stride,
+                                        const int32_t* plan_dev, const b200_decode_plan_info* info,
+                                        int num_heads, int kv_lora_rank, int rope_dim, float scale,
+                                        void* workspace, size_t workspace_bytes, void* out,
+                                        int out_is_f32, float* lse_out, int32_t* status,
+                                        void* stream) {
+  using namespace b200;
+  if (!info) {
+    set_last_error("mla_decode_absorbed: plan info is null");
+    return B200_EINVAL;
+  }
+  if (info->num_items == 0) return B200_OK;
+  if (!q_latent || !latent_cache || !block_table || !plan_dev || !out || !workspace ||
+      num_blocks <= 0 || num_heads <= 0) {
+    set_last_error("mla_decode_absorbed: null pointer or non-positive size");
+    return B200_EINVAL;
+  }
+  if (kv_lora_rank != kValueDim || rope_dim != kLatentDim - kValueDim) {
+    set_last_error("mla_decode_absorbed: latent %d+%d unsupported (kernel is built for 512+64)",
+                   kv_lora_rank, rope_dim);
+    return B200_EUNSUPPORTED;
+  }
+  if (num_heads > kMaxRows) {
+    set_last_error("mla_decode_absorbed: %d heads exceed the 16 query rows of one MMA tile", num_heads);
+    return B200_EUNSUPPORTED;
+  }
+  if (block_size < 8 || (block_size & (block_size - 1))) {
+    set_last_error("mla_decode_absorbed: block_size %d must be a power of two >= 8", block_size);
+    return B200_EUNSUPPORTED;
+  }
+  if (reinterpret_cast<uintptr_t>(q_latent) % 16 || (q_stride % 8) ||
+      q_stride < (int64_t)num_heads * kLatentDim || reinterpret_cast<uintptr_t>(out) % 16 ||
+      reinterpret_cast<uintptr_t>(workspace) % 16) {
+    set_last_error("mla_decode_absorbed: q, out and workspace must be 16-byte aligned, q stride a multiple of 8");
+    return B200_EALIGN;
+  }
+  const size_t need = (size_t)info->num_partials * (kMaxRows * (size_t)kValueDim + kMaxRows) * sizeof(float);
+  if (workspace_bytes < need) {
+    set_last_error("mla_decode_absorbed: workspace %zu bytes < %zu needed", workspace_bytes, need);
+    return B200_EPLAN;
+  }
+  const int box_tokens = block_size < kMlaTileTokens ? block_size : kMlaTileTokens;
+  CUtensorMap lat_map;
+  int rc = get_cache_tensor_map(latent_cache, num_blocks, block_size, 1, kLatentDim, box_tokens, &lat_map);
+  if (rc) return rc;
+
+  MlaParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q_latent);
+  p.q_stride = q_stride;
+  p.block_table = block_table;
+  p.bt_stride = bt_stride;
+  p.plan = plan_dev;
+  p.part_o = static_cast<float*>(workspace);
+  p.part_lse = p.part_o + (size_t)info->num_partials * kMaxRows * kValueDim;
+  p.out = out;
+  p.lse_out = lse_out;
+  p.status = status;
+  p.num_heads = num_heads;
+  p.block_size = block_size;
+  p.block_shift = __builtin_ctz(block_size);
+  p.num_blocks = num_blocks;
+  p.box_tokens = box_tokens;
+  p.boxes_per_tile = kMlaTileTokens / box_tokens;
+  p.out_is_f32 = out_is_f32;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t smem = sizeof(MlaSmem) + 1024;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 64 || !attr_set[dev]) {
+    rc = check_cuda(cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem),
+                    "mla_decode smem attribute");
+    if (rc) return rc;
+    if (dev < 64) attr_set[dev] = true;
+  }
+  mla_decode_kernel<<<info->num_ctas, kMlaThreads, smem, s>>>(lat_map, p);
+  rc = check_cuda(cudaGetLastError(), "mla_decode launch");
+  if (rc) return rc;
+  if (info->num_multi > 0) {
+    mla_merge_kernel<<<info->num_multi, 256, 0, s>>>(plan_dev, p.part_o, p.part_lse, out, lse_out,
+                                                     num_heads, out_is_f32);
+    rc = check_cuda(cudaGetLastError(), "mla_merge launch");
+  }
+  return rc;
+}

@@ -1,0 +1,148 @@
+"""Absorbed-MLA attention backend for B200 (DeepSeek-V2/V3, Moonlight).
+
+Same sub-block as auto-infer's ``mla_paged_absorbed``
+(auto_infer/layers/attention/mla.py:76-122): q projection (optionally through the
+q-LoRA), latent ``ckv = rms_norm(kv_a(x)[:kvl])`` plus the decoupled RoPE key,
+the query folded into latent space with W_UK, attention of all heads over ONE
+latent head of width kvl + rope, the first kvl output columns folded back with
+W_UV, then o_proj.  The two vendor calls in it (cache write, paged attention) go
+to the CUDA library; the latent is cached once per token instead of twice."""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .base import AttentionBackend
+from .gqa import rms_norm, rotate_half
+
+
+def ds_rope_interleave(x: torch.Tensor) -> torch.Tensor:
+    """DeepSeek stores the rotary dims interleaved; regroup them into halves
+    before the NeoX rotation (auto_infer/layers/rotary_embedding/__init__.py:15-23)."""
+    d = x.shape[-1]
+    return x.view(*x.shape[:-1], d // 2, 2).transpose(-1, -2).reshape(*x.shape[:-1], d)
+
+
+def build_absorb_weights(kv_b_weight, num_heads, qk_nope, v_head_dim, kv_lora_rank):
+    """kv_b_proj (H*(nope+vd), kvl) -> W_UK (H, nope, kvl), W_UV (H, vd, kvl)
+    (auto_infer/layers/attention/mla.py:67-73)."""
+    w = kv_b_weight.view(num_heads, qk_nope + v_head_dim, kv_lora_rank)
+    w_uk, w_uv = w.split([qk_nope, v_head_dim], dim=1)
+    return w_uk.contiguous(), w_uv.contiguous()
+
+
+class B200MlaBackend(AttentionBackend):
+    """Constructor keywords follow ``MlaFIABackend`` (mla.py:190-211).  Only the
+    absorbed form is built (``absorb`` must stay True): it is the one whose cache
+    is 9x smaller and whose attention is a single dense contraction."""
+
+    def __init__(self, w: dict, *, num_heads: int, qk_nope: int, qk_rope: int, v_head_dim: int,
+                 kv_lora_rank: int, q_lora_rank, rms_eps: float, softmax_scale: float,
+                 num_layers: int, device, dtype, absorb: bool = True, layer_prefix=None):
+        if not absorb:
+            raise NotImplementedError("the B200 MLA backend implements the absorbed latent form only")
+        self.w = w
+        self.num_heads = num_heads
+        self.qk_nope = qk_nope
+        self.qk_rope = qk_rope
+        self.v_head_dim = v_head_dim
+        self.kv_lora_rank = kv_lora_rank
+        self.q_lora_rank = q_lora_rank
+        self.rms_eps = rms_eps
+        self.softmax_scale = softmax_scale
+        self.num_layers = num_layers
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.absorb = True
+        self.layer_prefix = layer_prefix or (lambda i: f"model.layers.{i}.")
+        self._absorb_w: dict = {}
+
+    def alloc_kv_caches(self, num_blocks: int, block_size: int) -> list:
+        """Per layer ONE latent tensor (num_blocks, block_size, 1, kvl + rope),
+        returned as both members of the (k_cache, v_cache) pair the reference's
+        callers unpack (mla.py:214-219 allocates two)."""
+        shape = (num_blocks, block_size, 1, self.kv_lora_rank + self.qk_rope)
+        caches = []
+        for _ in range(self.num_layers):
+            latent = torch.zeros(shape, device=self.device, dtype=self.dtype)
+            caches.append((latent, latent))
+        return caches
+
+    def _weights(self, layer_idx: int):
+        if layer_idx not in self._absorb_w:
+            prefix = self.layer_prefix(layer_idx)
+            self._absorb_w[layer_idx] = build_absorb_weights(
+                self.w[prefix + "self_attn.kv_b_proj.weight"], self.num_heads, self.qk_nope,
+                self.v_head_dim, self.kv_lora_rank)
+        return self._absorb_w[layer_idx]
+
+    def attention(self, layer_idx: int, x: torch.Tensor, ctx) -> torch.Tensor:
+        w, prefix = self.w, self.layer_prefix(layer_idx)
+        t = x.shape[0]
+        nh, nope, rope, vd, kvl = (self.num_heads, self.qk_nope, self.qk_rope, self.v_head_dim,
+                                   self.kv_lora_rank)
+        if self.q_lora_rank is None:
+            q = x @ w[prefix + "self_attn.q_proj.weight"].t()
+        else:
+            q = rms_norm(x @ w[prefix + "self_attn.q_a_proj.weight"].t(),
+                         w[prefix + "self_attn.q_a_layernorm.weight"], self.rms_eps)
+            q = q @ w[prefix + "self_attn.q_b_proj.weight"].t()
+        q = q.view(t, nh, nope + rope)
+        q_nope, q_pe = q.split([nope, rope], dim=-1)
+        ckv_full = x @ w[prefix + "self_attn.kv_a_proj_with_mqa.weight"].t()
+        ckv, k_pe = ckv_full.split([kvl, rope], dim=-1)
+        ckv = rms_norm(ckv, w[prefix + "self_attn.kv_a_layernorm.weight"], self.rms_eps)
+        k_pe = k_pe.view(t, 1, rope)
+        q_pe = ds_rope_interleave(q_pe)
+        k_pe = ds_rope_interleave(k_pe)
+        q_pe = q_pe * ctx.cos + rotate_half(q_pe) * ctx.sin
+        k_pe = k_pe * ctx.cos + rotate_half(k_pe) * ctx.sin
+        w_uk, w_uv = self._weights(layer_idx)
+        q_latent = torch.cat([torch.einsum("tnp,npl->tnl", q_nope, w_uk), q_pe], dim=-1).contiguous()
+        k_latent = torch.cat([ckv.unsqueeze(1), k_pe], dim=-1).contiguous()
+        o_latent = self.latent_attention(layer_idx, q_latent, k_latent, ctx)
+        o = torch.einsum("tnl,nvl->tnv", o_latent, w_uv)
+        return o.reshape(t, nh * vd) @ w[prefix + "self_attn.o_proj.weight"].t()
+
+    # -- the accelerated part: latent write + latent attention --------------
+    def latent_attention(self, layer_idx: int, q_latent: torch.Tensor, k_latent: torch.Tensor,
+                         ctx) -> torch.Tensor:
+        latent_cache = ctx.kv_caches[layer_idx][0]
+        ops.reshape_and_cache(k_latent, None, latent_cache, None, ctx.slot_mapping)
+        plan, block_table = self._plan(ctx, q_latent.device)
+        return ops.mla_decode_absorbed(q_latent, latent_cache, block_table, plan,
+                                       self.softmax_scale, kv_lora_rank=self.kv_lora_rank)
+
+    def _plan(self, ctx, device):
+        """One plan per step.  The kernel takes q_len * heads <= 16 rows per
+        sequence; a longer query block (prefill chunk) is planned as q_len
+        single-token sequences that share the block-table row and end at
+        kv_len - q_len + 1 + i keys, which is the same bottom-right causal mask."""
+        cached = getattr(ctx, "_b200_mla_plan", None)
+        if cached is not None and cached[0] == (self.num_heads, str(device)):
+            return cached[1], cached[2]
+        cu, kv = list(ctx.cu_seqlens_q), list(ctx.seqlens_kv)
+        block_table = ctx.block_table
+        max_q = max(1, 16 // self.num_heads)
+        prev, wide = 0, False
+        for end in cu:
+            wide |= (end - prev) > max_q
+            prev = end
+        if wide:
+            new_cu, new_kv, rows = [], [], []
+            prev = acc = 0
+            for b, end in enumerate(cu):
+                q_len = end - prev
+                prev = end
+                for i in range(q_len):
+                    acc += 1
+                    new_cu.append(acc)
+                    new_kv.append(kv[b] - q_len + 1 + i)
+                    rows.append(b)
+            cu, kv = new_cu, new_kv
+            block_table = block_table.index_select(
+                0, torch.tensor(rows, dtype=torch.long, device=block_table.device))
+        plan = ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank)
+        assert plan.skipped_seqs == 0
+        setattr(ctx, "_b200_mla_plan", ((self.num_heads, str(device)), plan, block_table))
+        return plan, block_table

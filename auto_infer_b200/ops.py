@@ -166,6 +166,79 @@ def paged_decode_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torc
     return out
 
 
+class MlaDecodePlan:
+    """Host plan + device copy + workspace of the absorbed-MLA decode kernel
+    (32-token latent tiles, one shared latent head)."""
+
+    def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_heads: int,
+                 device, kv_lora_rank: int = 512, num_ctas: Optional[int] = None,
+                 causal_base: Optional[Sequence[int]] = None):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("MlaDecodePlan needs a CUDA device (no CPU fallback)")
+        num_seqs = len(cu_seqlens_q)
+        self.num_heads = num_heads
+        self.num_ctas = int(num_ctas) if num_ctas else sm_count(self.device)
+        nbytes = lib.b200_decode_plan_bytes(num_seqs, 1, self.num_ctas)
+        self.host = torch.empty(nbytes // 4, dtype=torch.int32, pin_memory=True)
+        cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
+        kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
+        base_ptr = None
+        if causal_base is not None:
+            base = torch.tensor(list(causal_base), dtype=torch.int32)
+            base_ptr = base.data_ptr()
+        self.info = DecodePlanInfo()
+        rc = lib.b200_mla_decode_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, num_seqs, num_heads,
+                                      self.num_ctas, self.host.data_ptr(), nbytes,
+                                      ctypes.byref(self.info))
+        _lib.check(rc, "b200_mla_decode_plan")
+        used = max(int(self.info.plan_ints), 16)
+        self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
+        self.dev.copy_(self.host[:used], non_blocking=True)
+        ws = (self.info.num_partials * (16 * kv_lora_rank + 16)) * 4 + 256
+        self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
+
+    @property
+    def skipped_seqs(self) -> int:
+        return int(self.info.skipped_seqs)
+
+
+def mla_decode_absorbed(q_latent: torch.Tensor, latent_cache: torch.Tensor,
+                        block_table: torch.Tensor, plan: MlaDecodePlan, scale: float,
+                        kv_lora_rank: int = 512, out: Optional[torch.Tensor] = None,
+                        out_f32: bool = False, lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Latent MQA attention of the absorbed MLA path
+    (auto_infer/layers/attention/mla.py:115-120): q_latent (T, H, kvl+rope) over
+    latent_cache (num_blocks, block_size, 1, kvl+rope) -> (T, H, kvl)."""
+    _need_cuda(q_latent, latent_cache, block_table)
+    lib = _lib.load()
+    t, h, width = q_latent.shape
+    if q_latent.stride(2) != 1 or q_latent.stride(1) != width:
+        q_latent = q_latent.contiguous()
+    if not latent_cache.is_contiguous():
+        raise ValueError("latent cache must be contiguous (num_blocks, block_size, 1, kvl+rope)")
+    num_blocks, block_size = latent_cache.shape[0], latent_cache.shape[1]
+    if block_table.dtype != torch.int32:
+        block_table = block_table.to(torch.int32)
+    if block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+    if out is None:
+        out = torch.empty(t, h, kv_lora_rank, dtype=torch.float32 if out_f32 else q_latent.dtype,
+                          device=q_latent.device)
+    with torch.cuda.device(q_latent.device):
+        rc = lib.b200_mla_decode_absorbed(
+            q_latent.data_ptr(), q_latent.stride(0), latent_cache.data_ptr(), num_blocks, block_size,
+            block_table.data_ptr(), block_table.stride(0), plan.dev.data_ptr(),
+            ctypes.byref(plan.info), h, kv_lora_rank, width - kv_lora_rank, float(scale),
+            plan.workspace.data_ptr(), plan.workspace.numel(), out.data_ptr(),
+            1 if out.dtype == torch.float32 else 0,
+            lse_out.data_ptr() if lse_out is not None else None,
+            status_word(q_latent.device).data_ptr(), _stream_ptr(q_latent.device))
+    _lib.check(rc, "b200_mla_decode_absorbed")
+    return out
+
+
 class PrefillPlan:
     """Host plan + device copy for the wide-query attention kernel: 128-row work
     items of every (sequence, kv head) pair whose q_len * group exceeds

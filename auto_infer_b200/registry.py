@@ -59,7 +59,22 @@ def _gqa_mtp(model, mode: str, prefix: str):
         w=model.w, layer_prefix=lambda _: prefix, rms_eps=cfg.rms_eps)
 
 
+def _mla(model, mode: str):
+    from .mla import B200MlaBackend
+    if mode == "dense":
+        _dense_unavailable("mla")
+    cfg = model.cfg
+    # the reference keeps the absorbed form off because its vendor op rejects a
+    # 576-wide head (auto_infer/models/deepseek_v2.py:62-64); here it is the form built
+    return B200MlaBackend(
+        model.w, num_heads=cfg.num_heads, qk_nope=cfg.qk_nope, qk_rope=cfg.qk_rope,
+        v_head_dim=cfg.v_head_dim, kv_lora_rank=cfg.kv_lora_rank, q_lora_rank=cfg.q_lora_rank,
+        rms_eps=cfg.rms_eps, softmax_scale=model._softmax_scale, num_layers=cfg.num_layers,
+        device=model.device, dtype=model.dtype, absorb=True, layer_prefix=model.layer_prefix)
+
+
 register_attention_family("gqa", _gqa)
+register_attention_family("mla", _mla)
 register_mtp_attention_family("gqa", _gqa_mtp)
 
 

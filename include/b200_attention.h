@@ -198,6 +198,38 @@ int b200_paged_decode_gqa_static(const void* q, int64_t q_stride,
                                  int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Absorbed-MLA decode attention over the latent cache.  Replaces the paged_fia
+ * call of mla_paged_absorbed (auto_infer/layers/attention/mla.py:115-120): one
+ * shared latent head of width kv_lora_rank + rope_dim = 512 + 64 per token,
+ * attended by all query heads, output = first kv_lora_rank columns.  The latent
+ * is cached ONCE, (num_blocks, block_size, 1, 576) bf16 (the reference keeps a
+ * second copy as V, mla.py:210-212, only because its vendor op wants symmetric
+ * K and V); the tile in shared memory serves as K and as V.
+ *   q_latent (T, H, 576) bf16 = [q_nope W_UK | q_pe], row stride q_stride
+ *   sequences need q_len * H <= 16 (plan with b200_mla_decode_plan, which uses
+ *   32-token tiles; buffers sized with b200_decode_plan_bytes(num_seqs, 1, ctas)
+ *   and b200_mla_decode_workspace_bytes)
+ *   out (T, H, 512) bf16 or fp32; lse_out (T, H) or NULL
+ * scale is the model's softmax scale, (qk_nope + qk_rope)^-0.5 * yarn factor
+ * (auto_infer/models/deepseek_v2.py:67,74), applied to the 576-wide products. */
+int b200_mla_decode_plan(const int32_t* cu_seqlens_q_host, const int32_t* seqlens_kv_host,
+                         const int32_t* causal_base_host,
+                         int num_seqs, int num_heads, int num_ctas,
+                         int32_t* plan_host, size_t plan_bytes,
+                         b200_decode_plan_info* info);
+
+size_t b200_mla_decode_workspace_bytes(int num_seqs, int num_ctas, int kv_lora_rank);
+
+int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
+                             const void* latent_cache, int num_blocks, int block_size,
+                             const int32_t* block_table, int64_t bt_stride,
+                             const int32_t* plan_dev, const b200_decode_plan_info* info,
+                             int num_heads, int kv_lora_rank, int rope_dim, float scale,
+                             void* workspace, size_t workspace_bytes,
+                             void* out, int out_is_f32, float* lse_out,
+                             int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Merge n_parts normalised partial results by log-sum-exp:
  *   o_parts (n_parts, rows, D) fp32, lse_parts (n_parts, rows) fp32 (natural
  *   log, -inf = empty part)  ->  out (rows, D) bf16 (or fp32 if out_is_f32),
