@@ -63,6 +63,15 @@ def measured_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s: the burst figure (kernels here are timed alone)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            return float(json.load(fh)["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
 def ncu_traffic(workload: str):
     """DRAM bytes per launch of the dominant kernel from the committed ncu
     summary (profiles/roofline_traffic.txt), or None."""
@@ -147,19 +156,9 @@ def time_events(fn, steps, warmup, pre=None):
     return out
 
 
-def side_config(name, device, flush):
-    """Kernel-only time of one smaller configuration: slot write + attention
-    captured in a CUDA graph (so host launch overhead is excluded), L2 flushed
-    before every replay."""
-    from auto_infer_b200 import ops, synth
-    b = synth.CONFIGS[name]().to(device)
-    plan = ops.DecodePlan(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, device)
-    out = torch.empty(b.q.shape, dtype=torch.bfloat16, device=device)
-
-    def step():
-        ops.reshape_and_cache(b.k_new, b.v_new, b.kv_cache[0], b.kv_cache[1], b.slot_mapping)
-        ops.paged_decode_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, plan, b.scale, out=out)
-
+def _graph_time(step, flush, iters=30):
+    """Median / best device time (us) of ``step`` replayed from a CUDA graph, L2
+    flushed before every replay (host launch overhead excluded)."""
     step()
     torch.cuda.synchronize()
     graph = torch.cuda.CUDAGraph()
@@ -169,14 +168,82 @@ def side_config(name, device, flush):
         with torch.cuda.graph(graph, stream=side):
             step()
     torch.cuda.synchronize()
-    times = time_events(graph.replay, 30, 5, pre=flush.zero_)
-    us = statistics.median(times) * 1e3
+    times = time_events(graph.replay, iters, 5, pre=flush.zero_)
+    return statistics.median(times) * 1e3, min(times) * 1e3
+
+
+def side_config(name, device, flush):
+    """Kernel-only time of one of the other configurations (slot write +
+    attention), with its roofline fractions against the measured peaks."""
+    from auto_infer_b200 import ops, synth
+    hbm_peak, _ = measured_peak()
+    tensor_peak = measured_tensor_peak()
+    if name.startswith("c3"):
+        batch = int(name.split("_b")[1])
+        b = synth.config3(batch, device)
+        plan = ops.MlaDecodePlan(b.cu_seqlens_q, b.seqlens_kv, 16, device)
+        out = torch.empty(b.num_tokens, 16, 512, dtype=torch.bfloat16, device=device)
+
+        def step():
+            ops.reshape_and_cache(b.k_new, None, b.kv_cache, None, b.slot_mapping)
+            ops.mla_decode_absorbed(b.q, b.kv_cache, b.block_table, plan, b.scale, out=out)
+
+        us, best = _graph_time(step, flush)
+        bytes_ = sum(b.seqlens_kv) * 1152 + b.num_tokens * 16 * (576 + 512) * 2
+        flops = sum(b.seqlens_kv) * 34816
+        return {"us_per_layer_step": round(us, 2), "best_us": round(best, 2),
+                "algorithmic_mb": round(bytes_ / 1e6, 2), "achieved_gbs": round(bytes_ / us / 1e3, 1),
+                "hbm_frac": round(bytes_ / us / 1e3 / hbm_peak, 3), "bound": "hbm",
+                "tflops": round(flops / us / 1e6, 1),
+                "tensor_frac": round(flops / us / 1e6 / tensor_peak, 4), "batch": batch}
+    if name == "c2":
+        b = synth.config2(device)
+        from auto_infer_b200.metadata import StepMetadata
+        meta = StepMetadata(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, device)
+        out = torch.empty(b.q.shape, dtype=torch.bfloat16, device=device)
+        k_cache, v_cache = b.kv_cache[0], b.kv_cache[1]
+
+        def write():
+            ops.reshape_and_cache(b.k_new, b.v_new, k_cache, v_cache, b.slot_mapping)
+
+        def decode():
+            ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, meta.decode, b.scale, out=out)
+
+        def prefill():
+            ops.paged_prefill_gqa(b.q, k_cache, v_cache, b.block_table, meta.prefill, b.scale, out=out)
+
+        def step():
+            write()
+            decode()
+            prefill()
+
+        us, best = _graph_time(step, flush)
+        us_dec, _ = _graph_time(decode, flush)
+        us_pre, _ = _graph_time(prefill, flush)
+        # causal-aware flops of the four 512-token chunks over prefixes 0/1024/2048/4096
+        flops = sum(4 * 32 * 128 * (512 * p + 131328) for p in (0, 1024, 2048, 4096))
+        dec_bytes = sum(b.seqlens_kv[:60]) * 4096 + 2 * 60 * 32 * 128 * 2
+        return {"us_per_layer_step": round(us, 2), "best_us": round(best, 2),
+                "decode_rows_us": round(us_dec, 2), "decode_rows_gbs": round(dec_bytes / us_dec / 1e3, 1),
+                "decode_rows_hbm_frac": round(dec_bytes / us_dec / 1e3 / hbm_peak, 3),
+                "prefill_chunks_us": round(us_pre, 2), "prefill_gflop": round(flops / 1e9, 2),
+                "prefill_tflops": round(flops / us_pre / 1e6, 1),
+                "prefill_tensor_frac": round(flops / us_pre / 1e6 / tensor_peak, 4),
+                "bound": "tensor (chunks) + hbm (decode rows)", "tokens": b.num_tokens}
+    b = synth.CONFIGS[name]().to(device)
+    plan = ops.DecodePlan(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, device)
+    out = torch.empty(b.q.shape, dtype=torch.bfloat16, device=device)
+
+    def step():
+        ops.reshape_and_cache(b.k_new, b.v_new, b.kv_cache[0], b.kv_cache[1], b.slot_mapping)
+        ops.paged_decode_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, plan, b.scale, out=out)
+
+    us, best = _graph_time(step, flush)
     bytes_ = b.kv_bytes() + 2 * b.q.numel() * 2
-    peak, _ = measured_peak()
-    return {"us_per_layer_step": round(us, 2), "best_us": round(min(times) * 1e3, 2),
+    return {"us_per_layer_step": round(us, 2), "best_us": round(best, 2),
             "algorithmic_mb": round(bytes_ / 1e6, 2), "achieved_gbs": round(bytes_ / us / 1e3, 1),
-            "hbm_frac": round(bytes_ / us / 1e3 / peak, 3), "batch": len(b.seqlens_kv),
-            "tokens": b.num_tokens}
+            "hbm_frac": round(bytes_ / us / 1e3 / hbm_peak, 3), "bound": "hbm",
+            "batch": len(b.seqlens_kv), "tokens": b.num_tokens}
 
 
 def cpu_baseline_sample(args, threads):
@@ -372,8 +439,9 @@ def main():
     if rank == 0 and world == 1:
         if not args.no_side_configs:
             flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-            for name in ("c1", "c4"):
+            for name in ("c1", "c2", "c3_b4", "c3_b16", "c3_b64", "c4"):
                 side[name] = side_config(name, device, flush)
+                torch.cuda.empty_cache()
             del flush
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
