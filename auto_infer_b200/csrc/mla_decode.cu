@@ -19,6 +19,7 @@
 // Algorithmic bytes per launch: sum_b kv_len_b * 1 152 B (+ q, o).
 #include "common.cuh"
 #include "decode_plan.h"
+#include "split_merge.cuh"
 
 namespace b200 {
 
@@ -221,16 +222,30 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
 
       float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
       if (gw < 2) {
-        // ---- S = Q K^T for this warp's 16 tokens over 576 dims
-#pragma unroll 4
-        for (int ks = 0; ks < kLatentDim / 16; ++ks) {
-          uint32_t qa[4], kb[4];
-          ldmatrix_x4(qa, qbase + ks * 32);
-          const int chunk = (ks & 3) * 2 + k_chunk_sel;
-          ldmatrix_x4(kb, sbase + (ks >> 2) * kMlaSubBytes + swz128(k_tok, chunk));
-          mma_bf16_16816(sacc[0], qa, kb[0], kb[1]);
-          mma_bf16_16816(sacc[1], qa, kb[2], kb[3]);
+        // ---- S = Q K^T for this warp's 16 tokens over 576 dims; four independent
+        // accumulator sets (one per k-step of a 64-dim sub-tile) keep the
+        // dependent mma chain at 9 instead of 36
+        float part[4][2][4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int n = 0; n < 2; ++n) part[u][n][0] = part[u][n][1] = part[u][n][2] = part[u][n][3] = 0.f;
+#pragma unroll 3
+        for (int sub = 0; sub < kMlaSub; ++sub) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint32_t qa[4], kb[4];
+            ldmatrix_x4(qa, qbase + (sub * 4 + u) * 32);
+            ldmatrix_x4(kb, sbase + sub * kMlaSubBytes + swz128(k_tok, u * 2 + k_chunk_sel));
+            mma_bf16_16816(part[u][0], qa, kb[0], kb[1]);
+            mma_bf16_16816(part[u][1], qa, kb[2], kb[3]);
+          }
         }
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            sacc[n][e] = (part[0][n][e] + part[1][n][e]) + (part[2][n][e] + part[3][n][e]);
         const int tok0 = tile * kMlaTileTokens + gw * 16 + qlane * 2;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -404,51 +419,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   }
 }
 
-// Merge of the partial (o, lse) records of sequences cut across CTAs: one CTA
-// of 256 threads per sequence, thread -> (row, 32 value columns).
-__global__ void __launch_bounds__(256)
-mla_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ part_o,
-                 const float* __restrict__ part_lse, void* __restrict__ out,
-                 float* __restrict__ lse_out, int num_heads, int out_is_f32) {
-  const MultiGroup g = reinterpret_cast<const MultiGroup*>(plan + plan[kHdrOffMulti])[blockIdx.x];
-  const int rows = g.q_len * num_heads;
-  const int row = threadIdx.x >> 4;
-  const int col0 = (threadIdx.x & 15) * 32;
-  if (row >= rows) return;
-  float mx = -INFINITY;
-  for (int pidx = g.part_begin; pidx < g.part_end; ++pidx)
-    mx = fmaxf(mx, part_lse[(int64_t)pidx * kMaxRows + row]);
-  float wsum = 0.f;
-  for (int pidx = g.part_begin; pidx < g.part_end; ++pidx) {
-    const float l = part_lse[(int64_t)pidx * kMaxRows + row];
-    wsum += (l == -INFINITY) ? 0.f : __expf(l - mx);
-  }
-  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-  const int64_t tok = g.q_start + row / num_heads;
-  const int head = row % num_heads;
-  for (int c = 0; c < 32; c += 4) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int pidx = g.part_begin; pidx < g.part_end; ++pidx) {
-      const float l = part_lse[(int64_t)pidx * kMaxRows + row];
-      const float wgt = (l == -INFINITY) ? 0.f : __expf(l - mx) * inv;
-      const float4 x = *reinterpret_cast<const float4*>(
-          part_o + ((int64_t)pidx * kMaxRows + row) * kValueDim + col0 + c);
-      acc.x += wgt * x.x; acc.y += wgt * x.y; acc.z += wgt * x.z; acc.w += wgt * x.w;
-    }
-    const int64_t off = (tok * num_heads + head) * kValueDim + col0 + c;
-    if (out_is_f32) {
-      *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + off) = acc;
-    } else {
-      uint2 pk;
-      pk.x = pack_bf16(acc.x, acc.y);
-      pk.y = pack_bf16(acc.z, acc.w);
-      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(out) + off) = pk;
-    }
-  }
-  if (lse_out && (threadIdx.x & 15) == 0)
-    lse_out[tok * num_heads + head] = wsum > 0.f ? mx + __logf(wsum) : -INFINITY;
-}
-
 }  // namespace b200
 
 extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
@@ -536,8 +506,8 @@ extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
   rc = check_cuda(cudaGetLastError(), "mla_decode launch");
   if (rc) return rc;
   if (info->num_multi > 0) {
-    mla_merge_kernel<<<info->num_multi, 256, 0, s>>>(plan_dev, p.part_o, p.part_lse, out, lse_out,
-                                                     num_heads, out_is_f32);
+    split_merge_kernel<kValueDim><<<split_merge_grid<kValueDim>(info->num_multi), 128, 0, s>>>(
+        plan_dev, p.part_o, p.part_lse, out, lse_out, num_heads, num_heads, out_is_f32);
     rc = check_cuda(cudaGetLastError(), "mla_merge launch");
   }
   return rc;

@@ -14,11 +14,12 @@
 //   * at the end of an item the eight warps merge their (m, l, O) through shared
 //     memory in a fixed order (deterministic) and write either the final bf16
 //     rows (the item covered the whole pair) or one fp32 partial (o, lse).
-// A second small kernel merges the partials of pairs that were cut.
+// A second small kernel (split_merge.cuh) merges the partials of pairs that were cut.
 //
 // Algorithmic bytes per launch: sum_b kv_len_b * 2 * Hkv * 128 * 2 B (+ q, o).
 #include "common.cuh"
 #include "decode_plan.h"
+#include "split_merge.cuh"
 
 namespace b200 {
 
@@ -435,53 +436,6 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   }
 }
 
-// Merges the partial (o, lse) records of (sequence, kv head) pairs that were cut
-// across CTAs.  One CTA of 256 threads per pair, thread -> (row, 8 columns).
-__global__ void __launch_bounds__(256)
-decode_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ part_o,
-                    const float* __restrict__ part_lse, void* __restrict__ out,
-                    float* __restrict__ lse_out, int num_q_heads, int group, int out_is_f32) {
-  const MultiGroup g = reinterpret_cast<const MultiGroup*>(plan + plan[kHdrOffMulti])[blockIdx.x];
-  const int rows = g.q_len * group;
-  const int t = threadIdx.x;
-  const int row = t >> 4;
-  const int col = (t & 15) * 8;
-  if (row >= rows) return;
-  float mx = -INFINITY;
-  for (int pidx = g.part_begin; pidx < g.part_end; ++pidx)
-    mx = fmaxf(mx, part_lse[(int64_t)pidx * kMaxRows + row]);
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  float wsum = 0.f;
-  for (int pidx = g.part_begin; pidx < g.part_end; ++pidx) {
-    const float l = part_lse[(int64_t)pidx * kMaxRows + row];
-    const float w = (l == -INFINITY) ? 0.f : __expf(l - mx);
-    wsum += w;
-    const float* src = part_o + ((int64_t)pidx * kMaxRows + row) * kHeadDim + col;
-    const float4 a = *reinterpret_cast<const float4*>(src);
-    const float4 b = *reinterpret_cast<const float4*>(src + 4);
-    acc[0] += w * a.x; acc[1] += w * a.y; acc[2] += w * a.z; acc[3] += w * a.w;
-    acc[4] += w * b.x; acc[5] += w * b.y; acc[6] += w * b.z; acc[7] += w * b.w;
-  }
-  const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] *= inv;
-  const int64_t tok = g.q_start + row / group;
-  const int head = g.kv_head * group + row % group;
-  const int64_t off = (tok * num_q_heads + head) * kHeadDim + col;
-  if (out_is_f32) {
-    float* dst = reinterpret_cast<float*>(out) + off;
-    *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-  } else {
-    uint4 pk;
-    pk.x = pack_bf16(acc[0], acc[1]); pk.y = pack_bf16(acc[2], acc[3]);
-    pk.z = pack_bf16(acc[4], acc[5]); pk.w = pack_bf16(acc[6], acc[7]);
-    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + off) = pk;
-  }
-  if (lse_out && (t & 15) == 0)
-    lse_out[tok * num_q_heads + head] = wsum > 0.f ? mx + __logf(wsum) : -INFINITY;
-}
-
 }  // namespace b200
 
 #ifdef B200_TRACE
@@ -578,8 +532,8 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
   rc = check_cuda(cudaGetLastError(), "paged_decode_gqa launch");
   if (rc) return rc;
   if (info->num_multi > 0) {
-    decode_merge_kernel<<<info->num_multi, 256, 0, s>>>(plan_dev, p.part_o, p.part_lse, out, lse_out,
-                                                        num_q_heads, p.group, out_is_f32);
+    split_merge_kernel<kHeadDim><<<split_merge_grid<kHeadDim>(info->num_multi), 128, 0, s>>>(
+        plan_dev, p.part_o, p.part_lse, out, lse_out, num_q_heads, p.group, out_is_f32);
     rc = check_cuda(cudaGetLastError(), "decode_merge launch");
   }
   return rc;
