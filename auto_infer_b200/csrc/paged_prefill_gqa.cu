@@ -13,10 +13,12 @@
 //     it skip the mask.
 // Tensor-bound: flops = 4 * D * sum over rows of visible keys.
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
 #include "decode_plan.h"
+#include "tc05.cuh"
 
 namespace b200 {
 
@@ -320,6 +322,329 @@ paged_prefill_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   }
 }
 
+
+// ============================================================================
+// tcgen05 version: one 128-row query tile per work item, S and O accumulated in
+// tensor memory by tcgen05.mma issued from one thread.
+//   warps 0-3  softmax + epilogue: thread r owns query row r (TMEM lane r)
+//   warp  4    TMA producer of 64-token K/V tiles (3-stage ring)
+//   warp  5    tensor-memory owner and MMA issuer
+// Per KV tile j: S_j = Q K_j^T (M 128, N 64, 8 x K16) into one of two S buffers,
+// softmax threads read their row with tcgen05.ld (no shuffles: a thread holds
+// the whole row), write P_j as bf16 in the 128-byte-swizzled K-major layout the
+// MMA reads, O (+)= P_j V_j (M 128, N 128, 4 x K16, V read MN-major from the
+// same TMA tile).  S_{j+1} is issued before P_j V_j so the tensor pipe works
+// while the softmax of tile j runs.  O is rescaled in tensor memory only when a
+// row maximum grows by more than 2^8 (the stale maximum is kept otherwise).
+// ============================================================================
+constexpr int kTcStages = 3;
+constexpr int kTcThreads = 192;
+constexpr int kTcTmemCols = 256;          // S0 [0,64) S1 [64,128) O [128,256)
+constexpr int kTcQBytes = 2 * kPfRows * 128;
+constexpr int kTcPBytes = kPfRows * 128;
+
+struct __align__(1024) TcSmem {
+  uint8_t q[kTcQBytes];                    // [dim half][128 rows][128 B], swizzled
+  uint8_t kv[kTcStages][kPfStageBytes];    // [K lo | K hi | V lo | V hi], 64 tokens x 128 B each
+  uint8_t p[kTcPBytes];                    // [128 rows][64 tokens x 2 B], swizzled
+  uint64_t kv_full[kTcStages];
+  uint64_t kv_empty[kTcStages];
+  uint64_t s_full[2];
+  uint64_t s_empty[2];
+  uint64_t p_full;
+  uint64_t pv_done;
+  uint64_t o_done;
+  uint64_t q_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(TcSmem) + 1024 <= 227 * 1024, "shared memory budget of one CTA");
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
+                        const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  TcSmem& sm = *reinterpret_cast<TcSmem*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(&sm.kv_full[s], 1);
+      mbar_init(&sm.kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.s_full[b], 1);
+      mbar_init(&sm.s_empty[b], 128);
+    }
+    mbar_init(&sm.p_full, 128);
+    mbar_init(&sm.pv_done, 1);
+    mbar_init(&sm.o_done, 1);
+    mbar_init(&sm.q_full, 128);
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(&sm.tmem_base, kTcTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (warp == 4) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&k_map);
+      tma_prefetch_desc(&v_map);
+    }
+    uint32_t it = 0;
+    const int nbox = p.boxes_per_tile;
+    for (int idx = blockIdx.x; idx < p.num_items; idx += gridDim.x) {
+      const PrefillItem item = p.items[idx];
+      const int last_block = (item.kv_len - 1) >> p.block_shift;
+      for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
+        int bid = 0;
+        if (lane < nbox) {
+          int lb = ((tile * kTileTokens) >> p.block_shift) + lane;
+          lb = lb > last_block ? last_block : lb;
+          bid = __ldg(p.block_table + (int64_t)item.seq * p.bt_stride + lb);
+        }
+        const int s = it % kTcStages;
+        if (lane == 0) {
+          mbar_wait_bounded(&sm.kv_empty[s], ((it / kTcStages) & 1u) ^ 1u, abort_flag, p.status);
+          mbar_arrive_expect_tx(&sm.kv_full[s], kPfStageBytes);
+        }
+        __syncwarp();
+        if (lane < nbox) {
+          if (bid < 0 || bid >= p.num_blocks) {
+            if (p.status) atomicOr(p.status, B200_STATUS_BAD_BLOCK);
+            bid = p.num_blocks;
+          }
+          const int tok = (tile * kTileTokens + lane * p.box_tokens) & (p.block_size - 1);
+          uint8_t* dst = sm.kv[s] + lane * p.box_tokens * 128;
+          tma_load_4d(dst, &k_map, &sm.kv_full[s], 0, item.kv_head, tok, bid);
+          tma_load_4d(dst + kPfHalfTileBytes, &k_map, &sm.kv_full[s], 64, item.kv_head, tok, bid);
+          tma_load_4d(dst + kPfTileBytes, &v_map, &sm.kv_full[s], 0, item.kv_head, tok, bid);
+          tma_load_4d(dst + kPfTileBytes + kPfHalfTileBytes, &v_map, &sm.kv_full[s], 64, item.kv_head, tok, bid);
+        }
+        __syncwarp();
+      }
+    }
+    if (lane == 0) {   // drain: nothing may still be landing when the CTA leaves
+      const uint32_t n = it < (uint32_t)kTcStages ? it : (uint32_t)kTcStages;
+      for (uint32_t k = 0; k < n; ++k) {
+        const uint32_t j = it - 1 - k;
+        mbar_wait_bounded(&sm.kv_full[j % kTcStages], (j / kTcStages) & 1u, abort_flag, p.status);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer ------------------------------
+    constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfRows, kTileTokens, false);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfRows, kPfHeadDim, true);
+    const uint32_t q_addr = smem_u32(sm.q);
+    const uint32_t p_addr = smem_u32(sm.p);
+    uint32_t it = 0;        // running tile counter (all roles count alike)
+    uint32_t item_no = 0;
+    auto issue_pv = [&](uint32_t jt, bool first_of_item) {
+      // O (+)= P V of running tile jt
+      const int s = jt % kTcStages;
+      mbar_wait_bounded(&sm.p_full, jt & 1u, abort_flag, p.status);
+      tc_fence_after();
+      const uint32_t v_addr = smem_u32(sm.kv[s]) + kPfTileBytes;
+#pragma unroll
+      for (int ks = 0; ks < kTileTokens / 16; ++ks) {
+        const uint64_t da = umma_desc_sw128(p_addr + ks * 32, 16, 1024);
+        const uint64_t db = umma_desc_sw128(v_addr + ks * 2048, kPfHalfTileBytes, 1024);
+        umma_bf16_ss(tmem + 128, da, db, idesc_pv, (first_of_item && ks == 0) ? 0u : 1u);
+      }
+      umma_commit(&sm.kv_empty[s]);
+      umma_commit(&sm.pv_done);
+    };
+    for (int idx = blockIdx.x; idx < p.num_items; idx += gridDim.x, ++item_no) {
+      const PrefillItem item = p.items[idx];
+      if (lane == 0) {
+        mbar_wait_bounded(&sm.q_full, item_no & 1u, abort_flag, p.status);
+        for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
+          const int s = it % kTcStages;
+          const int b = it & 1u;
+          mbar_wait_bounded(&sm.kv_full[s], (it / kTcStages) & 1u, abort_flag, p.status);
+          mbar_wait_bounded(&sm.s_empty[b], ((it >> 1) & 1u) ^ 1u, abort_flag, p.status);
+          tc_fence_after();
+          const uint32_t k_addr = smem_u32(sm.kv[s]);
+#pragma unroll
+          for (int ks = 0; ks < kPfHeadDim / 16; ++ks) {
+            const int half = ks >> 2;
+            const uint64_t da = umma_desc_sw128(q_addr + half * (kPfRows * 128) + (ks & 3) * 32, 16, 1024);
+            const uint64_t db = umma_desc_sw128(k_addr + half * kPfHalfTileBytes + (ks & 3) * 32, 16, 1024);
+            umma_bf16_ss(tmem + b * 64, da, db, idesc_qk, ks == 0 ? 0u : 1u);
+          }
+          umma_commit(&sm.s_full[b]);
+          if (tile > 0) issue_pv(it - 1, tile == 1);
+        }
+        if (item.n_tiles > 0) {
+          issue_pv(it - 1, item.n_tiles == 1);
+        }
+        umma_commit(&sm.o_done);
+      } else {
+        it += item.n_tiles;
+      }
+      __syncwarp();
+    }
+  } else {
+    // --------------------------- softmax + epilogue ---------------------------
+    const int r = threadIdx.x;                       // query row of the tile == TMEM lane
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const int G = p.group;
+    uint32_t it = 0;
+    uint32_t item_no = 0;
+    for (int idx = blockIdx.x; idx < p.num_items; idx += gridDim.x, ++item_no) {
+      const PrefillItem item = p.items[idx];
+      const int rows_total = item.q_len * G;
+      const int rg = item.row0 + r;
+      const bool valid = rg < rows_total;
+      const int64_t tok = item.q_start + (valid ? rg / G : 0);
+      const int head = item.kv_head * G + (valid ? rg % G : 0);
+      // ---- Q row -> shared memory (K-major, 128-byte swizzle), zero for unused rows
+      {
+        const uint4* src = reinterpret_cast<const uint4*>(p.q + tok * p.q_stride + (int64_t)head * kPfHeadDim);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (valid) v = __ldg(src + c);
+          *reinterpret_cast<uint4*>(sm.q + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v;
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&sm.q_full);
+      }
+      const int lim = valid ? min(item.causal_base + rg / G, item.kv_len - 1) : -1;
+      float m_used = -INFINITY;      // maximum the accumulators are scaled to (may lag behind the true one)
+      float l = 0.f;
+      for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
+        const int b = it & 1u;
+        mbar_wait_bounded(&sm.s_full[b], (it >> 1) & 1u, abort_flag, p.status);
+        tc_fence_after();
+        uint32_t sr[2][32];
+        tmem_ld32(lane_base + b * 64, sr[0]);
+        tmem_ld32(lane_base + b * 64 + 32, sr[1]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&sm.s_empty[b]);
+        const int tbase = tile * kTileTokens;
+        float mx = -INFINITY;
+        if (tbase + kTileTokens - 1 > lim) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < 32; ++c)
+              if (tbase + h * 32 + c > lim) sr[h][c] = __float_as_uint(-INFINITY);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sr[h][c]));
+        // lazy rescale: only when some row of the warp outgrew its stale maximum by 2^8
+        const bool grow = (mx - m_used) * p.scale_log2 > 8.f || (m_used == -INFINITY && mx > -INFINITY);
+        const bool rescale = __any_sync(0xffffffffu, grow);
+        float corr = 1.f;
+        if (rescale) {
+          const float m_new = fmaxf(m_used, mx);
+          corr = (m_used == -INFINITY) ? 0.f : fast_exp2((m_used - m_new) * p.scale_log2);
+          m_used = m_new;
+          l *= corr;
+        }
+        const float ms = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
+        uint32_t pk[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[h][c]), p.scale_log2, -ms));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[h][c + 1]), p.scale_log2, -ms));
+            l += p0 + p1;
+            pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
+          }
+        // P (single buffer) and O may be touched once P V of the previous tile is done
+        if (tile > 0) {
+          mbar_wait_bounded(&sm.pv_done, (it - 1) & 1u, abort_flag, p.status);
+          tc_fence_after();
+        }
+        if (rescale && tile > 0) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t orow[32];
+            tmem_ld32(lane_base + 128 + c * 32, orow);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
+            tmem_st32(lane_base + 128 + c * 32, orow);
+          }
+          tmem_wait_st();
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(sm.p + swz128(r, c)) =
+              make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&sm.p_full);
+      }
+      // ---- epilogue: O / l -> global
+      mbar_wait_bounded(&sm.o_done, item_no & 1u, abort_flag, p.status);
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t orow[32];
+          if (item.n_tiles > 0) {
+            tmem_ld32(lane_base + 128 + c * 32, orow);
+            tmem_wait_ld();
+          } else {                       // no visible key at all: the row reads as an empty part
+#pragma unroll
+            for (int i = 0; i < 32; ++i) orow[i] = 0u;
+          }
+          if (valid) {
+            const int64_t off = (tok * p.num_q_heads + head) * kPfHeadDim + c * 32;
+            if (p.out_is_f32) {
+              float* dst = reinterpret_cast<float*>(p.out) + off;
+#pragma unroll
+              for (int i = 0; i < 32; i += 4)
+                *reinterpret_cast<float4*>(dst + i) =
+                    make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
+                                __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+            } else {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
+                v.y = pack_bf16(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                v.z = pack_bf16(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
+                v.w = pack_bf16(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
+                *reinterpret_cast<uint4*>(dst + i) = v;
+              }
+            }
+          }
+        }
+      }
+      if (valid && p.lse_out)
+        p.lse_out[tok * p.num_q_heads + head] = l > 0.f ? m_used * p.scale + __logf(l) : -INFINITY;
+      tc_fence_before();
+    }
+  }
+  // ---- teardown: everyone is done with tensor memory before it is released
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kTcTmemCols);
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -445,6 +770,28 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
 
+  static const bool use_tc = [] {
+    const char* e = getenv("B200_PREFILL_TC");
+    return e && e[0] == '1';
+  }();
+  if (use_tc) {
+    const size_t smem_tc = sizeof(TcSmem) + 1024;
+    static bool attr_tc[64] = {false};
+    int dev_tc = 0;
+    cudaGetDevice(&dev_tc);
+    if (dev_tc >= 64 || !attr_tc[dev_tc]) {
+      rc = check_cuda(cudaFuncSetAttribute(paged_prefill_tc_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tc),
+                      "paged_prefill_tc smem attribute");
+      if (rc) return rc;
+      if (dev_tc < 64) attr_tc[dev_tc] = true;
+    }
+    int grid_tc = b200_sm_count();
+    if (grid_tc <= 0) grid_tc = 148;
+    if (grid_tc > info->num_items) grid_tc = info->num_items;
+    paged_prefill_tc_kernel<<<grid_tc, kTcThreads, smem_tc, static_cast<cudaStream_t>(stream)>>>(k_map, v_map, p);
+    return check_cuda(cudaGetLastError(), "paged_prefill_tc launch");
+  }
   const size_t smem = sizeof(PrefillSmem) + 1024;
   static bool attr_set[64] = {false};
   int dev = 0;

@@ -22,12 +22,18 @@ split_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ p
   const int rows = g.q_len * group;
   const int row = (blockIdx.x % kCtasPerPair) * kRowsPerCta + threadIdx.x / kThreadsPerRow;
   const int col = (threadIdx.x % kThreadsPerRow) * 4;
-  if (row >= rows) return;
+  if (row >= rows) return;          // warp-uniform: a warp never spans two rows
   const int n = g.part_end - g.part_begin;
   const float* lse_base = part_lse + (int64_t)g.part_begin * kMaxRows + row;
   const float* o_base = part_o + ((int64_t)g.part_begin * kMaxRows + row) * kDim + col;
+  // The lse values of the row are fetched 32 at a time, one per lane (all lanes of
+  // a warp work on the same row), so the maximum costs one round of loads and a
+  // shuffle tree instead of n dependent loads; the weights then travel by shuffle.
+  const int lane = threadIdx.x & 31;
   float mx = -INFINITY;
-  for (int i = 0; i < n; ++i) mx = fmaxf(mx, lse_base[(int64_t)i * kMaxRows]);
+  for (int i = lane; i < n; i += 32) mx = fmaxf(mx, lse_base[(int64_t)i * kMaxRows]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   float4 acc[4];
   float wsum[4];
 #pragma unroll
@@ -35,15 +41,22 @@ split_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ p
     acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     wsum[u] = 0.f;
   }
-  for (int i = 0; i < n; i += 4) {
+  for (int base = 0; base < n; base += 32) {
+    float wl = 0.f;
+    if (base + lane < n) {
+      const float l = lse_base[(int64_t)(base + lane) * kMaxRows];
+      wl = (l == -INFINITY) ? 0.f : __expf(l - mx);
+    }
+    const int cnt = min(32, n - base);
+    for (int i = 0; i < cnt; i += 4) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (i + u < n) {
-        const float l = lse_base[(int64_t)(i + u) * kMaxRows];
-        const float w = (l == -INFINITY) ? 0.f : __expf(l - mx);
-        const float4 x = *reinterpret_cast<const float4*>(o_base + (int64_t)(i + u) * kMaxRows * kDim);
-        wsum[u] += w;
-        acc[u].x += w * x.x; acc[u].y += w * x.y; acc[u].z += w * x.z; acc[u].w += w * x.w;
+      for (int u = 0; u < 4; ++u) {
+        const float w = __shfl_sync(0xffffffffu, wl, (i + u) & 31);
+        if (i + u < cnt) {
+          const float4 x = *reinterpret_cast<const float4*>(o_base + (int64_t)(base + i + u) * kMaxRows * kDim);
+          wsum[u] += w;
+          acc[u].x += w * x.x; acc[u].y += w * x.y; acc[u].z += w * x.z; acc[u].w += w * x.w;
+        }
       }
     }
   }
