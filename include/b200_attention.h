@@ -44,6 +44,7 @@ extern "C" {
 #define B200_STATUS_BAD_SLOT      1   /* slot outside [0, num_blocks*block_size)   */
 #define B200_STATUS_BAD_BLOCK     2   /* block id outside [0, num_blocks)          */
 #define B200_STATUS_WAIT_TIMEOUT  4   /* a bounded barrier wait ran out            */
+#define B200_STATUS_BAD_LAUNCH    8   /* a kernel found its launch state unusable  */
 
 /* Library / build identification: "b200-attention <ver> sm_100a". */
 const char* b200_version(void);
