@@ -37,6 +37,7 @@ struct PrefillParams {
   const int32_t* block_table;
   int64_t bt_stride;
   const PrefillItem* items;
+  int* work_counter;                // two plan words: next item to hand out, CTAs that have left
   int num_items;
   void* out;
   float* lse_out;
@@ -79,6 +80,9 @@ struct __align__(1024) TcSmem {
   uint64_t pv_done;
   uint64_t o_done;
   uint64_t q_full;
+  uint64_t item_full[2];                   // work-queue hand-off: producer warp -> MMA and softmax roles
+  uint64_t item_empty[2];
+  int next_item[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -111,6 +115,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     mbar_init(&sm.pv_done, 1);
     mbar_init(&sm.o_done, 1);
     mbar_init(&sm.q_full, 128);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.item_full[b], 1);
+      mbar_init(&sm.item_empty[b], 129);   // 128 softmax threads + the MMA thread
+    }
     mbar_fence_init();
   }
   if (warp == 5) {
@@ -122,6 +130,15 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
   volatile int* abort_flag = &sm.abort_flag;
+  // Items are handed out dynamically, longest first: the producer warp draws the
+  // next index from a global counter and passes it to the other roles through a
+  // two-slot mailbox.  -1 ends the CTA.
+  auto take_item = [&](uint32_t k) -> int {
+    mbar_wait_bounded(&sm.item_full[k & 1u], (k >> 1) & 1u, abort_flag, p.status);
+    const int idx = *reinterpret_cast<volatile int*>(&sm.next_item[k & 1u]);
+    mbar_arrive(&sm.item_empty[k & 1u]);
+    return (*abort_flag || idx < 0 || idx >= p.num_items) ? -1 : idx;
+  };
 
   if (warp == 4) {
     // ------------------------------ TMA producer ------------------------------
@@ -131,7 +148,17 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     uint32_t it = 0;
     const int nbox = p.boxes_per_tile;
-    for (int idx = blockIdx.x; idx < p.num_items; idx += gridDim.x) {
+    for (uint32_t k = 0;; ++k) {
+      int idx = -1;
+      if (lane == 0) {
+        idx = atomicAdd(p.work_counter, 1);
+        if (idx >= p.num_items || *abort_flag) idx = -1;
+        mbar_wait_bounded(&sm.item_empty[k & 1u], ((k >> 1) & 1u) ^ 1u, abort_flag, p.status);
+        sm.next_item[k & 1u] = idx;
+        mbar_arrive(&sm.item_full[k & 1u]);     // release semantics: the index is visible to waiters
+      }
+      idx = __shfl_sync(0xffffffffu, idx, 0);
+      if (idx < 0) break;
       const PrefillItem item = p.items[idx];
       const int last_block = (item.kv_len - 1) >> p.block_shift;
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
@@ -192,9 +219,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       umma_commit(&sm.kv_empty[s]);
       umma_commit(&sm.pv_done);
     };
-    for (int idx = blockIdx.x; idx < p.num_items; idx += gridDim.x, ++item_no) {
-      const PrefillItem item = p.items[idx];
-      if (lane == 0) {
+    if (lane == 0) {
+      for (;; ++item_no) {
+        const int idx = take_item(item_no);
+        if (idx < 0) break;
+        const PrefillItem item = p.items[idx];
         mbar_wait_bounded(&sm.q_full, item_no & 1u, abort_flag, p.status);
         for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
           const int s = it % kTcStages;
@@ -217,11 +246,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           issue_pv(it - 1, item.n_tiles == 1);
         }
         umma_commit(&sm.o_done);
-      } else {
-        it += item.n_tiles;
       }
-      __syncwarp();
     }
+    __syncwarp();
   } else {
     // --------------------------- softmax + epilogue ---------------------------
     const int r = threadIdx.x;                       // query row of the tile == TMEM lane
@@ -229,7 +256,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     const int G = p.group;
     uint32_t it = 0;
     uint32_t item_no = 0;
-    for (int idx = blockIdx.x; idx < p.num_items; idx += gridDim.x, ++item_no) {
+    for (;; ++item_no) {
+      const int idx = take_item(item_no);
+      if (idx < 0) break;
       const PrefillItem item = p.items[idx];
       const int rows_total = item.q_len * G;
       const int rg = item.row0 + r;
@@ -371,6 +400,15 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     tc_fence_after();
     tmem_dealloc(tmem, kTcTmemCols);
   }
+  // the last CTA to leave puts the queue back to zero for the next launch on this plan
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.work_counter + 1, 1) == (int)gridDim.x - 1) {
+      p.work_counter[0] = 0;
+      p.work_counter[1] = 0;
+      __threadfence();
+    }
+  }
 }
 
 }  // namespace b200
@@ -443,7 +481,7 @@ extern "C" int b200_prefill_plan(const int32_t* cu_q, const int32_t* kv_lens,
 extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const void* key_cache,
                                       const void* value_cache, int num_blocks, int block_size,
                                       const int32_t* block_table, int64_t bt_stride,
-                                      const int32_t* plan_dev, const b200_prefill_plan_info* info,
+                                      int32_t* plan_dev, const b200_prefill_plan_info* info,
                                       int num_q_heads, int num_kv_heads, int head_dim, float scale,
                                       void* out, int out_is_f32, float* lse_out, int32_t* status,
                                       void* stream) {
@@ -483,6 +521,7 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   p.block_table = block_table;
   p.bt_stride = bt_stride;
   p.items = reinterpret_cast<const PrefillItem*>(plan_dev + kPlanHeaderInts);
+  p.work_counter = plan_dev + 2;
   p.num_items = info->num_items;
   p.out = out;
   p.lse_out = lse_out;

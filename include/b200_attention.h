@@ -140,7 +140,10 @@ int b200_paged_decode_gqa(const void* q, int64_t q_stride,
  *   min_rows: only sequences with q_len * (Hq/Hkv) > min_rows are planned
  *             (16 complements b200_decode_plan; 0 plans every sequence).
  * Arguments of the run call are those of b200_paged_decode_gqa without the
- * workspace (this kernel needs none). */
+ * workspace (this kernel needs none).  plan_dev is not const: two of its header
+ * words serve as the kernel's work-queue counters and are back at zero when the
+ * kernel ends, so one plan serves all layers of a step as long as the calls that
+ * share it do not overlap on the GPU. */
 typedef struct b200_prefill_plan_info {
   int32_t num_items;       /* 128-row work items                               */
   int32_t total_tiles;     /* 64-token KV tiles summed over the items          */
@@ -160,7 +163,7 @@ int b200_paged_prefill_gqa(const void* q, int64_t q_stride,
                            const void* key_cache, const void* value_cache,
                            int num_blocks, int block_size,
                            const int32_t* block_table, int64_t bt_stride,
-                           const int32_t* plan_dev, const b200_prefill_plan_info* info,
+                           int32_t* plan_dev, const b200_prefill_plan_info* info,
                            int num_q_heads, int num_kv_heads, int head_dim, float scale,
                            void* out, int out_is_f32, float* lse_out,
                            int32_t* status, void* stream);

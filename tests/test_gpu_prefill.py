@@ -15,8 +15,14 @@ def _prefill(q, kc, vc, bt, cu, kv, scale, n_q, n_kv, min_rows=0, want_lse=False
     plan = ops.PrefillPlan(cu, kv, n_q, n_kv, "cuda", min_rows=min_rows)
     lse = torch.empty(q.shape[0], n_q, dtype=torch.float32, device="cuda") if want_lse else None
     out = torch.zeros(q.shape, dtype=torch.bfloat16, device="cuda")
-    ops.paged_prefill_gqa(q.cuda(), kc.cuda(), vc.cuda(), bt.cuda(), plan, scale, out=out, lse_out=lse)
+    qd, kd, vd, btd = q.cuda(), kc.cuda(), vc.cuda(), bt.cuda()
+    ops.paged_prefill_gqa(qd, kd, vd, btd, plan, scale, out=out, lse_out=lse)
+    # the same plan serves every layer of a step: a second launch must find the
+    # work queue reset and reproduce the result bit for bit
+    again = torch.zeros_like(out)
+    ops.paged_prefill_gqa(qd, kd, vd, btd, plan, scale, out=again)
     torch.cuda.synchronize()
+    assert torch.equal(out, again)
     assert ops.read_status("cuda") == 0
     return (out.cpu(), lse.cpu()) if want_lse else out.cpu()
 
