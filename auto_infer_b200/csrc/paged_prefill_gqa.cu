@@ -5,8 +5,8 @@
 // Work item = 128 packed query rows of one (sequence, kv head) pair, a row being
 // (query position, head within the kv group), so the G heads that share a kv
 // head also share every K/V tile in shared memory.  Items are sorted by
-// decreasing key count on the host and dealt round-robin to the resident CTAs
-// (two per SM, so one CTA's softmax overlaps the other's MMAs).
+// decreasing key count on the host and handed out through a work queue to one
+// persistent CTA per SM.
 // Tensor-bound: flops = 4 * D * sum over rows of visible keys.
 #include <algorithm>
 #include <vector>
@@ -21,7 +21,6 @@ constexpr int kPfHeadDim = 128;
 constexpr int kPfRows = 128;                                   // packed query rows per item
 constexpr int kPfHalfTileBytes = kTileTokens * 128;
 constexpr int kPfTileBytes = 2 * kPfHalfTileBytes;
-constexpr int kPfStageBytes = 2 * kPfTileBytes;
 constexpr int kPfItemInts = 8;
 constexpr int kPfMagic = 0x70663030;
 
@@ -46,14 +45,27 @@ struct PrefillParams {
   int block_size, block_shift, num_blocks, box_tokens, boxes_per_tile;
   int out_is_f32;
   float scale, scale_log2;
+#ifdef B200_TRACE
+  long long* trace;                 // clock64 samples of CTA 0 (debug builds)
+#endif
 };
+
+#ifdef B200_TRACE
+#define PF_TRACE(slot, tileno, code)                                                          \
+  do {                                                                                        \
+    if (p.trace && blockIdx.x == 0 && (tileno) < 64) p.trace[(tileno) * 16 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define PF_TRACE(slot, tileno, code) do {} while (0)
+#endif
 
 // ============================================================================
 // One 128-row query tile per work item, S and O accumulated in tensor memory by
 // tcgen05.mma issued from one thread.
 //   warps 0-3  softmax + epilogue: thread r owns query row r (TMEM lane r)
-//   warp  4    TMA producer of 64-token K/V tiles (2-stage ring)
-//   warp  5    tensor-memory owner and MMA issuer
+//   warp  4    TMA producer of 64-token K and V tiles (two 5-stage rings)
+//   warp  5    tensor-memory owner, issues S = Q K^T
+//   warp  6    issues O += P V
 // Per KV tile j: S_j = Q K_j^T (M 128, N 64, 8 x K16) into one of two S buffers,
 // softmax threads read their row with tcgen05.ld (no shuffles: a thread holds
 // the whole row), write P_j as bf16 in the 128-byte-swizzled K-major layout the
@@ -62,18 +74,21 @@ struct PrefillParams {
 // while the softmax of tile j runs.  O is rescaled in tensor memory only when a
 // row maximum grows by more than 2^8 (the stale maximum is kept otherwise).
 // ============================================================================
-constexpr int kTcStages = 2;
-constexpr int kTcThreads = 192;
+constexpr int kTcStages = 5;          // K ring and V ring, 16 KB per stage each
+constexpr int kTcThreads = 224;
 constexpr int kTcTmemCols = 256;          // S0 [0,64) S1 [64,128) O [128,256)
 constexpr int kTcQBytes = 2 * kPfRows * 128;
 constexpr int kTcPBytes = kPfRows * 128;
 
 struct __align__(1024) TcSmem {
   uint8_t q[kTcQBytes];                    // [dim half][128 rows][128 B], swizzled
-  uint8_t kv[kTcStages][kPfStageBytes];    // [K lo | K hi | V lo | V hi], 64 tokens x 128 B each
+  uint8_t k[kTcStages][kPfTileBytes];      // [dims 0-63 | dims 64-127], 64 tokens x 128 B each
+  uint8_t v[kTcStages][kPfTileBytes];
   uint8_t p[kTcPBytes];                    // [128 rows][64 tokens x 2 B], swizzled
-  uint64_t kv_full[kTcStages];
-  uint64_t kv_empty[kTcStages];
+  uint64_t k_full[kTcStages];
+  uint64_t k_empty[kTcStages];
+  uint64_t v_full[kTcStages];
+  uint64_t v_empty[kTcStages];
   uint64_t s_full[2];
   uint64_t s_empty[2];
   uint64_t p_full;
@@ -86,10 +101,9 @@ struct __align__(1024) TcSmem {
   uint32_t tmem_base;
   int abort_flag;
 };
-// two CTAs per SM: 2 x (dynamic + 1 KB reserved) must fit the SM's 228 KB
-static_assert(sizeof(TcSmem) <= 113 * 1024, "shared memory budget for two CTAs per SM");
+static_assert(sizeof(TcSmem) <= 227 * 1024, "shared memory budget of one CTA");
 
-__global__ void __launch_bounds__(kTcThreads, 2)
+__global__ void __launch_bounds__(kTcThreads, 1)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
                         const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -104,8 +118,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
     for (int s = 0; s < kTcStages; ++s) {
-      mbar_init(&sm.kv_full[s], 1);
-      mbar_init(&sm.kv_empty[s], 1);
+      mbar_init(&sm.k_full[s], 1);
+      mbar_init(&sm.k_empty[s], 1);
+      mbar_init(&sm.v_full[s], 1);
+      mbar_init(&sm.v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.s_full[b], 1);
@@ -117,7 +133,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     mbar_init(&sm.q_full, 128);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.item_full[b], 1);
-      mbar_init(&sm.item_empty[b], 129);   // 128 softmax threads + the MMA thread
+      mbar_init(&sm.item_empty[b], 130);   // 128 softmax threads + the two MMA threads
     }
     mbar_fence_init();
   }
@@ -169,22 +185,33 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           bid = __ldg(p.block_table + (int64_t)item.seq * p.bt_stride + lb);
         }
         const int s = it % kTcStages;
+        const uint32_t ph = ((it / kTcStages) & 1u) ^ 1u;
+        if (bid < 0 || bid >= p.num_blocks) {
+          if (lane < nbox && p.status) atomicOr(p.status, B200_STATUS_BAD_BLOCK);
+          bid = p.num_blocks;
+        }
+        const int tok = (tile * kTileTokens + lane * p.box_tokens) & (p.block_size - 1);
+        // K and V travel through separate rings: a K stage is free again as soon as
+        // S = Q K^T has run, one step earlier than the V stage of the same tile
         if (lane == 0) {
-          mbar_wait_bounded(&sm.kv_empty[s], ((it / kTcStages) & 1u) ^ 1u, abort_flag, p.status);
-          mbar_arrive_expect_tx(&sm.kv_full[s], kPfStageBytes);
+          mbar_wait_bounded(&sm.k_empty[s], ph, abort_flag, p.status);
+          mbar_arrive_expect_tx(&sm.k_full[s], kPfTileBytes);
         }
         __syncwarp();
         if (lane < nbox) {
-          if (bid < 0 || bid >= p.num_blocks) {
-            if (p.status) atomicOr(p.status, B200_STATUS_BAD_BLOCK);
-            bid = p.num_blocks;
-          }
-          const int tok = (tile * kTileTokens + lane * p.box_tokens) & (p.block_size - 1);
-          uint8_t* dst = sm.kv[s] + lane * p.box_tokens * 128;
-          tma_load_4d(dst, &k_map, &sm.kv_full[s], 0, item.kv_head, tok, bid);
-          tma_load_4d(dst + kPfHalfTileBytes, &k_map, &sm.kv_full[s], 64, item.kv_head, tok, bid);
-          tma_load_4d(dst + kPfTileBytes, &v_map, &sm.kv_full[s], 0, item.kv_head, tok, bid);
-          tma_load_4d(dst + kPfTileBytes + kPfHalfTileBytes, &v_map, &sm.kv_full[s], 64, item.kv_head, tok, bid);
+          uint8_t* dst = sm.k[s] + lane * p.box_tokens * 128;
+          tma_load_4d(dst, &k_map, &sm.k_full[s], 0, item.kv_head, tok, bid);
+          tma_load_4d(dst + kPfHalfTileBytes, &k_map, &sm.k_full[s], 64, item.kv_head, tok, bid);
+        }
+        if (lane == 0) {
+          mbar_wait_bounded(&sm.v_empty[s], ph, abort_flag, p.status);
+          mbar_arrive_expect_tx(&sm.v_full[s], kPfTileBytes);
+        }
+        __syncwarp();
+        if (lane < nbox) {
+          uint8_t* dst = sm.v[s] + lane * p.box_tokens * 128;
+          tma_load_4d(dst, &v_map, &sm.v_full[s], 0, item.kv_head, tok, bid);
+          tma_load_4d(dst + kPfHalfTileBytes, &v_map, &sm.v_full[s], 64, item.kv_head, tok, bid);
         }
         __syncwarp();
       }
@@ -193,57 +220,75 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       const uint32_t n = it < (uint32_t)kTcStages ? it : (uint32_t)kTcStages;
       for (uint32_t k = 0; k < n; ++k) {
         const uint32_t j = it - 1 - k;
-        mbar_wait_bounded(&sm.kv_full[j % kTcStages], (j / kTcStages) & 1u, abort_flag, p.status);
+        mbar_wait_bounded(&sm.k_full[j % kTcStages], (j / kTcStages) & 1u, abort_flag, p.status);
+        mbar_wait_bounded(&sm.v_full[j % kTcStages], (j / kTcStages) & 1u, abort_flag, p.status);
       }
     }
   } else if (warp == 5) {
-    // ------------------------------ MMA issuer ------------------------------
-    constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfRows, kTileTokens, false);
-    constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfRows, kPfHeadDim, true);
-    const uint32_t q_addr = smem_u32(sm.q);
-    const uint32_t p_addr = smem_u32(sm.p);
-    uint32_t it = 0;        // running tile counter (all roles count alike)
-    uint32_t item_no = 0;
-    auto issue_pv = [&](uint32_t jt, bool first_of_item) {
-      // O (+)= P V of running tile jt
-      const int s = jt % kTcStages;
-      mbar_wait_bounded(&sm.p_full, jt & 1u, abort_flag, p.status);
-      tc_fence_after();
-      const uint32_t v_addr = smem_u32(sm.kv[s]) + kPfTileBytes;
-#pragma unroll
-      for (int ks = 0; ks < kTileTokens / 16; ++ks) {
-        const uint64_t da = umma_desc_sw128(p_addr + ks * 32, 16, 1024);
-        const uint64_t db = umma_desc_sw128(v_addr + ks * 2048, kPfHalfTileBytes, 1024);
-        umma_bf16_ss(tmem + 128, da, db, idesc_pv, (first_of_item && ks == 0) ? 0u : 1u);
-      }
-      umma_commit(&sm.kv_empty[s]);
-      umma_commit(&sm.pv_done);
-    };
+    // ------------------------- MMA issuer: S = Q K^T -------------------------
+    // Two threads issue the MMAs, one per GEMM, so that S of the next tile is
+    // queued while the other thread still waits for P of the current one.
     if (lane == 0) {
-      for (;; ++item_no) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfRows, kTileTokens, false);
+      // descriptors differ only in their start-address field: build once, add offsets
+      const uint64_t dq = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
+      const uint64_t dk = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024);
+      uint32_t it = 0;
+      for (uint32_t item_no = 0;; ++item_no) {
         const int idx = take_item(item_no);
         if (idx < 0) break;
-        const PrefillItem item = p.items[idx];
+        const int n_tiles = p.items[idx].n_tiles;
         mbar_wait_bounded(&sm.q_full, item_no & 1u, abort_flag, p.status);
-        for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
+        for (int tile = 0; tile < n_tiles; ++tile, ++it) {
           const int s = it % kTcStages;
           const int b = it & 1u;
-          mbar_wait_bounded(&sm.kv_full[s], (it / kTcStages) & 1u, abort_flag, p.status);
+          PF_TRACE(8, it, 0);
+          mbar_wait_bounded(&sm.k_full[s], (it / kTcStages) & 1u, abort_flag, p.status);
+          PF_TRACE(9, it, 0);
           mbar_wait_bounded(&sm.s_empty[b], ((it >> 1) & 1u) ^ 1u, abort_flag, p.status);
           tc_fence_after();
-          const uint32_t k_addr = smem_u32(sm.kv[s]);
+          PF_TRACE(10, it, 0);
+          const uint64_t dks = dk + (uint64_t)((s * kPfTileBytes) >> 4);
+          const uint32_t d_tmem = tmem + b * 64;
 #pragma unroll
           for (int ks = 0; ks < kPfHeadDim / 16; ++ks) {
             const int half = ks >> 2;
-            const uint64_t da = umma_desc_sw128(q_addr + half * (kPfRows * 128) + (ks & 3) * 32, 16, 1024);
-            const uint64_t db = umma_desc_sw128(k_addr + half * kPfHalfTileBytes + (ks & 3) * 32, 16, 1024);
-            umma_bf16_ss(tmem + b * 64, da, db, idesc_qk, ks == 0 ? 0u : 1u);
+            umma_bf16_ss(d_tmem, dq + (uint64_t)((half * (kPfRows * 128) + (ks & 3) * 32) >> 4),
+                         dks + (uint64_t)((half * kPfHalfTileBytes + (ks & 3) * 32) >> 4), idesc_qk,
+                         ks == 0 ? 0u : 1u);
           }
           umma_commit(&sm.s_full[b]);
-          if (tile > 0) issue_pv(it - 1, tile == 1);
+          umma_commit(&sm.k_empty[s]);
+          PF_TRACE(11, it, 0);
         }
-        if (item.n_tiles > 0) {
-          issue_pv(it - 1, item.n_tiles == 1);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 6) {
+    // ------------------------- MMA issuer: O += P V --------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfRows, kPfHeadDim, true);
+      const uint64_t dp = umma_desc_sw128(smem_u32(sm.p), 16, 1024);
+      const uint64_t dv = umma_desc_sw128(smem_u32(sm.v[0]), kPfHalfTileBytes, 1024);
+      uint32_t it = 0;
+      for (uint32_t item_no = 0;; ++item_no) {
+        const int idx = take_item(item_no);
+        if (idx < 0) break;
+        const int n_tiles = p.items[idx].n_tiles;
+        for (int tile = 0; tile < n_tiles; ++tile, ++it) {
+          const int s = it % kTcStages;
+          mbar_wait_bounded(&sm.v_full[s], (it / kTcStages) & 1u, abort_flag, p.status);
+          mbar_wait_bounded(&sm.p_full, it & 1u, abort_flag, p.status);
+          tc_fence_after();
+          PF_TRACE(13, it, 0);
+          const uint64_t dvs = dv + (uint64_t)((s * kPfTileBytes) >> 4);
+#pragma unroll
+          for (int ks = 0; ks < kTileTokens / 16; ++ks)
+            umma_bf16_ss(tmem + 128, dp + (uint64_t)((ks * 32) >> 4), dvs + (uint64_t)((ks * 2048) >> 4),
+                         idesc_pv, (tile == 0 && ks == 0) ? 0u : 1u);
+          umma_commit(&sm.v_empty[s]);
+          umma_commit(&sm.pv_done);
+          PF_TRACE(12, it, 0);
         }
         umma_commit(&sm.o_done);
       }
@@ -282,14 +327,17 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       float l = 0.f;
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
         const int b = it & 1u;
+        if (r == 0) PF_TRACE(0, it, 0);
         mbar_wait_bounded(&sm.s_full[b], (it >> 1) & 1u, abort_flag, p.status);
         tc_fence_after();
+        if (r == 0) PF_TRACE(1, it, 0);
         uint32_t sr[2][32];
         tmem_ld32(lane_base + b * 64, sr[0]);
         tmem_ld32(lane_base + b * 64 + 32, sr[1]);
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive(&sm.s_empty[b]);
+        if (r == 0) PF_TRACE(2, it, 0);
         const int tbase = tile * kTileTokens;
         float mx = -INFINITY;
         if (tbase + kTileTokens - 1 > lim) {
@@ -299,10 +347,15 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             for (int c = 0; c < 32; ++c)
               if (tbase + h * 32 + c > lim) sr[h][c] = __float_as_uint(-INFINITY);
         }
+        {
+          float mq[8];                      // eight independent chains instead of one of 64
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+          for (int u = 0; u < 8; ++u) mq[u] = __uint_as_float(sr[0][u]);
 #pragma unroll
-          for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sr[h][c]));
+          for (int c = 8; c < 64; ++c) mq[c & 7] = fmaxf(mq[c & 7], __uint_as_float(sr[c >> 5][c & 31]));
+          mx = fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])),
+                     fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
+        }
         // lazy rescale: only when some row of the warp outgrew its stale maximum by 2^8
         const bool grow = (mx - m_used) * p.scale_log2 > 8.f || (m_used == -INFINITY && mx > -INFINITY);
         const bool rescale = __any_sync(0xffffffffu, grow);
@@ -315,20 +368,24 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         }
         const float ms = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
         uint32_t pk[32];
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
             const float p0 = fast_exp2(fmaf(__uint_as_float(sr[h][c]), p.scale_log2, -ms));
             const float p1 = fast_exp2(fmaf(__uint_as_float(sr[h][c + 1]), p.scale_log2, -ms));
-            l += p0 + p1;
+            ls[(c >> 1) & 3] += p0 + p1;
             pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
           }
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        if (r == 0) PF_TRACE(3, it, 0);
         // P (single buffer) and O may be touched once P V of the previous tile is done
         if (tile > 0) {
           mbar_wait_bounded(&sm.pv_done, (it - 1) & 1u, abort_flag, p.status);
           tc_fence_after();
         }
+        if (r == 0) PF_TRACE(4, it, 0);
         if (rescale && tile > 0) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
@@ -345,9 +402,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         for (int c = 0; c < 8; ++c)
           *reinterpret_cast<uint4*>(sm.p + swz128(r, c)) =
               make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
+        if (r == 0) PF_TRACE(5, it, 0);
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(&sm.p_full);
+        if (r == 0) PF_TRACE(6, it, 0);
       }
       // ---- epilogue: O / l -> global
       mbar_wait_bounded(&sm.o_done, item_no & 1u, abort_flag, p.status);
@@ -478,6 +537,11 @@ extern "C" int b200_prefill_plan(const int32_t* cu_q, const int32_t* kv_lens,
   return B200_OK;
 }
 
+#ifdef B200_TRACE
+static long long* g_pf_trace = nullptr;
+extern "C" void b200_debug_set_pf_trace(void* dev_ptr) { g_pf_trace = static_cast<long long*>(dev_ptr); }
+#endif
+
 extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const void* key_cache,
                                       const void* value_cache, int num_blocks, int block_size,
                                       const int32_t* block_table, int64_t bt_stride,
@@ -536,6 +600,9 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   p.out_is_f32 = out_is_f32;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
+#ifdef B200_TRACE
+  p.trace = g_pf_trace;
+#endif
 
   const size_t smem_tc = sizeof(TcSmem);
   static bool attr_tc[64] = {false};
@@ -550,7 +617,6 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   }
   int grid = b200_sm_count();
   if (grid <= 0) grid = 148;
-  grid *= 2;                                   // two resident CTAs per SM
   if (grid > info->num_items) grid = info->num_items;
   paged_prefill_tc_kernel<<<grid, kTcThreads, smem_tc, static_cast<cudaStream_t>(stream)>>>(k_map, v_map, p);
   return check_cuda(cudaGetLastError(), "paged_prefill_gqa launch");
