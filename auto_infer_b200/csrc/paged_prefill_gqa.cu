@@ -19,8 +19,9 @@ namespace b200 {
 
 constexpr int kPfHeadDim = 128;
 constexpr int kPfRows = 128;                                   // packed query rows per item
-constexpr int kPfHalfTileBytes = kTileTokens * 128;
-constexpr int kPfTileBytes = 2 * kPfHalfTileBytes;
+constexpr int kPfTile = 128;                                    // KV tokens per tile
+constexpr int kPfHalfTileBytes = kPfTile * 128;                 // [128 tokens][64 dims] bf16
+constexpr int kPfTileBytes = 2 * kPfHalfTileBytes;              // K or V tile: 32 KB
 constexpr int kPfItemInts = 8;
 constexpr int kPfMagic = 0x70663030;
 
@@ -51,51 +52,63 @@ struct PrefillParams {
 };
 
 #ifdef B200_TRACE
-#define PF_TRACE(slot, tileno, code)                                                          \
+#define PF_TRACE(slot, tileno)                                                                \
   do {                                                                                        \
-    if (p.trace && blockIdx.x == 0 && (tileno) < 64) p.trace[(tileno) * 16 + (slot)] = clock64(); \
+    if (p.trace && blockIdx.x == 0 && (tileno) < 96) p.trace[(tileno) * 16 + (slot)] = clock64(); \
   } while (0)
 #else
-#define PF_TRACE(slot, tileno, code) do {} while (0)
+#define PF_TRACE(slot, tileno) do {} while (0)
 #endif
+
 
 // ============================================================================
 // One 128-row query tile per work item, S and O accumulated in tensor memory by
-// tcgen05.mma issued from one thread.
-//   warps 0-3  softmax + epilogue: thread r owns query row r (TMEM lane r)
-//   warp  4    TMA producer of 64-token K and V tiles (two 5-stage rings)
-//   warp  5    tensor-memory owner, issues S = Q K^T
-//   warp  6    issues O += P V
-// Per KV tile j: S_j = Q K_j^T (M 128, N 64, 8 x K16) into one of two S buffers,
-// softmax threads read their row with tcgen05.ld (no shuffles: a thread holds
-// the whole row), write P_j as bf16 in the 128-byte-swizzled K-major layout the
-// MMA reads, O (+)= P_j V_j (M 128, N 128, 4 x K16, V read MN-major from the
-// same TMA tile).  S_{j+1} is issued before P_j V_j so the tensor pipe works
-// while the softmax of tile j runs.  O is rescaled in tensor memory only when a
-// row maximum grows by more than 2^8 (the stale maximum is kept otherwise).
+// tcgen05.mma.  Warp roles (352 threads, one CTA per SM):
+//   warps 0-3   softmax group A     thread r owns query row r (TMEM lane r)
+//   warps 4-7   softmax group B     same rows, the other half of the KV tiles
+//   warp  8     TMA producer of 64-token K and V tiles (separate rings)
+//   warp  9     tensor-memory owner, issues S = Q K^T
+//   warp  10    issues O += P V
+// Per 128-token KV tile j: S_j = Q K_j^T (M 128, N 128, 8 x K16) lands in one of
+// two S buffers; group g owns columns [64 g, 64 g + 64) of it (tokens 64 g ... of
+// the tile): its threads read their row with tcgen05.ld (a thread holds a whole
+// row: no shuffles), write P as bf16 in the 128-byte-swizzled K-major layout, and
+// O_g (+)= P_g V_j[64 g ...] (M 128, N 128, 4 x K16, V read MN-major from the TMA
+// tile) accumulates in the group's own O buffer under the group's own running
+// maximum.  The groups are thus a split of the keys; their (m, l, O) are merged
+// at the end of an item, each group writing half of the output columns.  The
+// MMAs are queued by two dedicated threads, so S of the next tile is in flight
+// while the exponentials of this one run.  O is rescaled in tensor memory only
+// when a row maximum grows by more than 2^8 (the stale maximum is kept otherwise).
+// N = 128 per MMA on purpose: a tcgen05.mma costs ~50 cycles to issue whatever its
+// size, so N = 64 instructions (32 cycles of math) would leave the pipe waiting.
 // ============================================================================
-constexpr int kTcStages = 5;          // K ring and V ring, 16 KB per stage each
-constexpr int kTcThreads = 224;
-constexpr int kTcTmemCols = 256;          // S0 [0,64) S1 [64,128) O [128,256)
+constexpr int kTcKStages = 2;             // 32 KB per stage
+constexpr int kTcVStages = 3;
+constexpr int kTcSoftmaxThreads = 256;
+constexpr int kTcThreads = kTcSoftmaxThreads + 96;
+constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O_A [256,384) O_B [384,512)
 constexpr int kTcQBytes = 2 * kPfRows * 128;
 constexpr int kTcPBytes = kPfRows * 128;
 
 struct __align__(1024) TcSmem {
   uint8_t q[kTcQBytes];                    // [dim half][128 rows][128 B], swizzled
-  uint8_t k[kTcStages][kPfTileBytes];      // [dims 0-63 | dims 64-127], 64 tokens x 128 B each
-  uint8_t v[kTcStages][kPfTileBytes];
-  uint8_t p[kTcPBytes];                    // [128 rows][64 tokens x 2 B], swizzled
-  uint64_t k_full[kTcStages];
-  uint64_t k_empty[kTcStages];
-  uint64_t v_full[kTcStages];
-  uint64_t v_empty[kTcStages];
+  uint8_t k[kTcKStages][kPfTileBytes];     // [dims 0-63 | dims 64-127], 128 tokens x 128 B each
+  uint8_t v[kTcVStages][kPfTileBytes];
+  uint8_t p[2][kTcPBytes];                 // per group: [128 rows][64 tokens x 2 B], swizzled
+  float row_m[2][kPfRows];                 // end-of-item exchange of the groups' row state
+  float row_l[2][kPfRows];
+  uint64_t k_full[kTcKStages];
+  uint64_t k_empty[kTcKStages];
+  uint64_t v_full[kTcVStages];
+  uint64_t v_empty[kTcVStages];
   uint64_t s_full[2];
   uint64_t s_empty[2];
-  uint64_t p_full;
-  uint64_t pv_done;
+  uint64_t p_full[2];
+  uint64_t pv_done[2];
   uint64_t o_done;
   uint64_t q_full;
-  uint64_t item_full[2];                   // work-queue hand-off: producer warp -> MMA and softmax roles
+  uint64_t item_full[2];                   // work-queue hand-off: producer warp -> the other roles
   uint64_t item_empty[2];
   int next_item[2];
   uint32_t tmem_base;
@@ -117,27 +130,27 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
-    for (int s = 0; s < kTcStages; ++s) {
+    for (int s = 0; s < kTcKStages; ++s) {
       mbar_init(&sm.k_full[s], 1);
       mbar_init(&sm.k_empty[s], 1);
+    }
+    for (int s = 0; s < kTcVStages; ++s) {
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.s_full[b], 1);
-      mbar_init(&sm.s_empty[b], 128);
-    }
-    mbar_init(&sm.p_full, 128);
-    mbar_init(&sm.pv_done, 1);
-    mbar_init(&sm.o_done, 1);
-    mbar_init(&sm.q_full, 128);
-    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.s_empty[b], kTcSoftmaxThreads);
+      mbar_init(&sm.p_full[b], 128);
+      mbar_init(&sm.pv_done[b], 1);
       mbar_init(&sm.item_full[b], 1);
-      mbar_init(&sm.item_empty[b], 130);   // 128 softmax threads + the two MMA threads
+      mbar_init(&sm.item_empty[b], kTcSoftmaxThreads + 2);   // softmax threads + the two MMA threads
     }
+    mbar_init(&sm.o_done, 1);
+    mbar_init(&sm.q_full, kTcSoftmaxThreads);
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&sm.tmem_base, kTcTmemCols);
     tmem_relinquish();
   }
@@ -156,7 +169,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     return (*abort_flag || idx < 0 || idx >= p.num_items) ? -1 : idx;
   };
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&k_map);
@@ -179,60 +192,60 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       const int last_block = (item.kv_len - 1) >> p.block_shift;
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
         int bid = 0;
+        const int token0 = tile * kPfTile + lane * p.box_tokens;     // first token of this lane's box
         if (lane < nbox) {
-          int lb = ((tile * kTileTokens) >> p.block_shift) + lane;
-          lb = lb > last_block ? last_block : lb;
+          int lb = token0 >> p.block_shift;
+          lb = lb > last_block ? last_block : lb;                  // tail boxes re-read the last valid page
           bid = __ldg(p.block_table + (int64_t)item.seq * p.bt_stride + lb);
         }
-        const int s = it % kTcStages;
-        const uint32_t ph = ((it / kTcStages) & 1u) ^ 1u;
         if (bid < 0 || bid >= p.num_blocks) {
           if (lane < nbox && p.status) atomicOr(p.status, B200_STATUS_BAD_BLOCK);
           bid = p.num_blocks;
         }
-        const int tok = (tile * kTileTokens + lane * p.box_tokens) & (p.block_size - 1);
+        const int tok = token0 & (p.block_size - 1);
         // K and V travel through separate rings: a K stage is free again as soon as
         // S = Q K^T has run, one step earlier than the V stage of the same tile
+        const int sk = it % kTcKStages, sv = it % kTcVStages;
         if (lane == 0) {
-          mbar_wait_bounded(&sm.k_empty[s], ph, abort_flag, p.status);
-          mbar_arrive_expect_tx(&sm.k_full[s], kPfTileBytes);
+          mbar_wait_bounded(&sm.k_empty[sk], ((it / kTcKStages) & 1u) ^ 1u, abort_flag, p.status);
+          mbar_arrive_expect_tx(&sm.k_full[sk], kPfTileBytes);
         }
         __syncwarp();
         if (lane < nbox) {
-          uint8_t* dst = sm.k[s] + lane * p.box_tokens * 128;
-          tma_load_4d(dst, &k_map, &sm.k_full[s], 0, item.kv_head, tok, bid);
-          tma_load_4d(dst + kPfHalfTileBytes, &k_map, &sm.k_full[s], 64, item.kv_head, tok, bid);
+          uint8_t* dst = sm.k[sk] + lane * p.box_tokens * 128;
+          tma_load_4d(dst, &k_map, &sm.k_full[sk], 0, item.kv_head, tok, bid);
+          tma_load_4d(dst + kPfHalfTileBytes, &k_map, &sm.k_full[sk], 64, item.kv_head, tok, bid);
         }
         if (lane == 0) {
-          mbar_wait_bounded(&sm.v_empty[s], ph, abort_flag, p.status);
-          mbar_arrive_expect_tx(&sm.v_full[s], kPfTileBytes);
+          mbar_wait_bounded(&sm.v_empty[sv], ((it / kTcVStages) & 1u) ^ 1u, abort_flag, p.status);
+          mbar_arrive_expect_tx(&sm.v_full[sv], kPfTileBytes);
         }
         __syncwarp();
         if (lane < nbox) {
-          uint8_t* dst = sm.v[s] + lane * p.box_tokens * 128;
-          tma_load_4d(dst, &v_map, &sm.v_full[s], 0, item.kv_head, tok, bid);
-          tma_load_4d(dst + kPfHalfTileBytes, &v_map, &sm.v_full[s], 64, item.kv_head, tok, bid);
+          uint8_t* dst = sm.v[sv] + lane * p.box_tokens * 128;
+          tma_load_4d(dst, &v_map, &sm.v_full[sv], 0, item.kv_head, tok, bid);
+          tma_load_4d(dst + kPfHalfTileBytes, &v_map, &sm.v_full[sv], 64, item.kv_head, tok, bid);
         }
         __syncwarp();
       }
     }
     if (lane == 0) {   // drain: nothing may still be landing when the CTA leaves
-      const uint32_t n = it < (uint32_t)kTcStages ? it : (uint32_t)kTcStages;
-      for (uint32_t k = 0; k < n; ++k) {
+      for (uint32_t k = 0; k < (uint32_t)kTcVStages && k < it; ++k) {
         const uint32_t j = it - 1 - k;
-        mbar_wait_bounded(&sm.k_full[j % kTcStages], (j / kTcStages) & 1u, abort_flag, p.status);
-        mbar_wait_bounded(&sm.v_full[j % kTcStages], (j / kTcStages) & 1u, abort_flag, p.status);
+        if (k < (uint32_t)kTcKStages)
+          mbar_wait_bounded(&sm.k_full[j % kTcKStages], (j / kTcKStages) & 1u, abort_flag, p.status);
+        mbar_wait_bounded(&sm.v_full[j % kTcVStages], (j / kTcVStages) & 1u, abort_flag, p.status);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------- MMA issuer: S = Q K^T -------------------------
-    // Two threads issue the MMAs, one per GEMM, so that S of the next tile is
-    // queued while the other thread still waits for P of the current one.
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfRows, kTileTokens, false);
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfRows, kPfTile, false);
       // descriptors differ only in their start-address field: build once, add offsets
       const uint64_t dq = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
       const uint64_t dk = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024);
+      const uint32_t dq_lo = (uint32_t)dq, dq_hi = (uint32_t)(dq >> 32);
+      const uint32_t dk_lo = (uint32_t)dk, dk_hi = (uint32_t)(dk >> 32);
       uint32_t it = 0;
       for (uint32_t item_no = 0;; ++item_no) {
         const int idx = take_item(item_no);
@@ -240,55 +253,65 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         const int n_tiles = p.items[idx].n_tiles;
         mbar_wait_bounded(&sm.q_full, item_no & 1u, abort_flag, p.status);
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
-          const int s = it % kTcStages;
+          const int s = it % kTcKStages;
           const int b = it & 1u;
-          PF_TRACE(8, it, 0);
-          mbar_wait_bounded(&sm.k_full[s], (it / kTcStages) & 1u, abort_flag, p.status);
-          PF_TRACE(9, it, 0);
+          mbar_wait_bounded(&sm.k_full[s], (it / kTcKStages) & 1u, abort_flag, p.status);
           mbar_wait_bounded(&sm.s_empty[b], ((it >> 1) & 1u) ^ 1u, abort_flag, p.status);
           tc_fence_after();
-          PF_TRACE(10, it, 0);
-          const uint64_t dks = dk + (uint64_t)((s * kPfTileBytes) >> 4);
-          const uint32_t d_tmem = tmem + b * 64;
+          const uint32_t k_lo = dk_lo + (uint32_t)((s * kPfTileBytes) >> 4);
+          const uint32_t d_tmem = tmem + b * 128;
+          umma_bf16_ss_lo<false>(d_tmem, dq_lo, dq_hi, k_lo, dk_hi, idesc_qk);
 #pragma unroll
-          for (int ks = 0; ks < kPfHeadDim / 16; ++ks) {
+          for (int ks = 1; ks < kPfHeadDim / 16; ++ks) {
             const int half = ks >> 2;
-            umma_bf16_ss(d_tmem, dq + (uint64_t)((half * (kPfRows * 128) + (ks & 3) * 32) >> 4),
-                         dks + (uint64_t)((half * kPfHalfTileBytes + (ks & 3) * 32) >> 4), idesc_qk,
-                         ks == 0 ? 0u : 1u);
+            umma_bf16_ss_lo<true>(d_tmem, dq_lo + (uint32_t)((half * (kPfRows * 128) + (ks & 3) * 32) >> 4),
+                                  dq_hi, k_lo + (uint32_t)((half * kPfHalfTileBytes + (ks & 3) * 32) >> 4),
+                                  dk_hi, idesc_qk);
           }
           umma_commit(&sm.s_full[b]);
           umma_commit(&sm.k_empty[s]);
-          PF_TRACE(11, it, 0);
+          PF_TRACE(4, it);
         }
       }
     }
     __syncwarp();
-  } else if (warp == 6) {
+  } else if (warp == 10) {
     // ------------------------- MMA issuer: O += P V --------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfRows, kPfHeadDim, true);
-      const uint64_t dp = umma_desc_sw128(smem_u32(sm.p), 16, 1024);
+      const uint64_t dp = umma_desc_sw128(smem_u32(sm.p[0]), 16, 1024);
       const uint64_t dv = umma_desc_sw128(smem_u32(sm.v[0]), kPfHalfTileBytes, 1024);
+      const uint32_t dp_lo = (uint32_t)dp, dp_hi = (uint32_t)(dp >> 32);
+      const uint32_t dv_lo = (uint32_t)dv, dv_hi = (uint32_t)(dv >> 32);
       uint32_t it = 0;
       for (uint32_t item_no = 0;; ++item_no) {
         const int idx = take_item(item_no);
         if (idx < 0) break;
         const int n_tiles = p.items[idx].n_tiles;
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
-          const int s = it % kTcStages;
-          mbar_wait_bounded(&sm.v_full[s], (it / kTcStages) & 1u, abort_flag, p.status);
-          mbar_wait_bounded(&sm.p_full, it & 1u, abort_flag, p.status);
-          tc_fence_after();
-          PF_TRACE(13, it, 0);
-          const uint64_t dvs = dv + (uint64_t)((s * kPfTileBytes) >> 4);
+          const int s = it % kTcVStages;
+          mbar_wait_bounded(&sm.v_full[s], (it / kTcVStages) & 1u, abort_flag, p.status);
+          const uint32_t v_lo = dv_lo + (uint32_t)((s * kPfTileBytes) >> 4);
 #pragma unroll
-          for (int ks = 0; ks < kTileTokens / 16; ++ks)
-            umma_bf16_ss(tmem + 128, dp + (uint64_t)((ks * 32) >> 4), dvs + (uint64_t)((ks * 2048) >> 4),
-                         idesc_pv, (tile == 0 && ks == 0) ? 0u : 1u);
+          for (int g = 0; g < 2; ++g) {
+            mbar_wait_bounded(&sm.p_full[g], it & 1u, abort_flag, p.status);
+            tc_fence_after();
+            PF_TRACE(5 + g * 4, it);
+            const uint32_t p_lo = dp_lo + (uint32_t)((g * kTcPBytes) >> 4);
+            const uint32_t vg_lo = v_lo + (uint32_t)((g * 64 * 128) >> 4);   // the group's 64 tokens of the tile
+            const uint32_t d_tmem = tmem + 256 + g * 128;
+            if (tile == 0)                                  // first tile of the item overwrites
+              umma_bf16_ss_lo<false>(d_tmem, p_lo, dp_hi, vg_lo, dv_hi, idesc_pv);
+            else
+              umma_bf16_ss_lo<true>(d_tmem, p_lo, dp_hi, vg_lo, dv_hi, idesc_pv);
+#pragma unroll
+            for (int ks = 1; ks < 4; ++ks)
+              umma_bf16_ss_lo<true>(d_tmem, p_lo + (uint32_t)((ks * 32) >> 4), dp_hi,
+                                    vg_lo + (uint32_t)((ks * 2048) >> 4), dv_hi, idesc_pv);
+            umma_commit(&sm.pv_done[g]);
+          }
           umma_commit(&sm.v_empty[s]);
-          umma_commit(&sm.pv_done);
-          PF_TRACE(12, it, 0);
+          PF_TRACE(6, it);
         }
         umma_commit(&sm.o_done);
       }
@@ -296,12 +319,15 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     __syncwarp();
   } else {
     // --------------------------- softmax + epilogue ---------------------------
-    const int r = threadIdx.x;                       // query row of the tile == TMEM lane
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    const int g = warp >> 2;                         // group: tokens [64 g, 64 g + 64) of every KV tile
+    const int r = threadIdx.x & 127;                 // query row of the tile == TMEM lane
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t s_col = lane_base + g * 64;       // + 128 * (tile & 1)
+    const uint32_t o_col = lane_base + 256 + g * 128;
+    uint8_t* p_buf = sm.p[g];
     const int G = p.group;
     uint32_t it = 0;
-    uint32_t item_no = 0;
-    for (;; ++item_no) {
+    for (uint32_t item_no = 0;; ++item_no) {
       const int idx = take_item(item_no);
       if (idx < 0) break;
       const PrefillItem item = p.items[idx];
@@ -310,43 +336,44 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       const bool valid = rg < rows_total;
       const int64_t tok = item.q_start + (valid ? rg / G : 0);
       const int head = item.kv_head * G + (valid ? rg % G : 0);
-      // ---- Q row -> shared memory (K-major, 128-byte swizzle), zero for unused rows
+      // ---- Q row -> shared memory (K-major, 128-byte swizzle), zero for unused rows;
+      // each group copies one 64-dim half of the row
       {
-        const uint4* src = reinterpret_cast<const uint4*>(p.q + tok * p.q_stride + (int64_t)head * kPfHeadDim);
+        const uint4* src = reinterpret_cast<const uint4*>(p.q + tok * p.q_stride + (int64_t)head * kPfHeadDim) + g * 8;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
+        for (int c = 0; c < 8; ++c) {
           uint4 v = make_uint4(0u, 0u, 0u, 0u);
           if (valid) v = __ldg(src + c);
-          *reinterpret_cast<uint4*>(sm.q + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v;
+          *reinterpret_cast<uint4*>(sm.q + g * (kPfRows * 128) + swz128(r, c)) = v;
         }
         fence_proxy_async_smem();
         mbar_arrive(&sm.q_full);
       }
       const int lim = valid ? min(item.causal_base + rg / G, item.kv_len - 1) : -1;
-      float m_used = -INFINITY;      // maximum the accumulators are scaled to (may lag behind the true one)
+      float m_used = -INFINITY;      // maximum the group's accumulators are scaled to (may lag behind)
       float l = 0.f;
+      bool have_o = false;           // this group has issued at least one P V for the item
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
-        const int b = it & 1u;
-        if (r == 0) PF_TRACE(0, it, 0);
-        mbar_wait_bounded(&sm.s_full[b], (it >> 1) & 1u, abort_flag, p.status);
+        const int sb = it & 1u;                      // S buffer of this tile
+        if (r == 0) PF_TRACE(0 + g * 10, it);
+        mbar_wait_bounded(&sm.s_full[sb], (it >> 1) & 1u, abort_flag, p.status);
         tc_fence_after();
-        if (r == 0) PF_TRACE(1, it, 0);
+        if (r == 0) PF_TRACE(1 + g * 10, it);
         uint32_t sr[2][32];
-        tmem_ld32(lane_base + b * 64, sr[0]);
-        tmem_ld32(lane_base + b * 64 + 32, sr[1]);
+        tmem_ld32(s_col + sb * 128, sr[0]);
+        tmem_ld32(s_col + sb * 128 + 32, sr[1]);
         tmem_wait_ld();
         tc_fence_before();
-        mbar_arrive(&sm.s_empty[b]);
-        if (r == 0) PF_TRACE(2, it, 0);
-        const int tbase = tile * kTileTokens;
-        float mx = -INFINITY;
-        if (tbase + kTileTokens - 1 > lim) {
+        mbar_arrive(&sm.s_empty[sb]);
+        const int tbase = tile * kPfTile + g * 64;   // first token of this group's columns
+        if (tbase + 63 > lim) {
 #pragma unroll
           for (int h = 0; h < 2; ++h)
 #pragma unroll
             for (int c = 0; c < 32; ++c)
               if (tbase + h * 32 + c > lim) sr[h][c] = __float_as_uint(-INFINITY);
         }
+        float mx;
         {
           float mq[8];                      // eight independent chains instead of one of 64
 #pragma unroll
@@ -379,83 +406,100 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
           }
         l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-        if (r == 0) PF_TRACE(3, it, 0);
-        // P (single buffer) and O may be touched once P V of the previous tile is done
-        if (tile > 0) {
-          mbar_wait_bounded(&sm.pv_done, (it - 1) & 1u, abort_flag, p.status);
+        if (r == 0) PF_TRACE(2 + g * 10, it);
+        // the group's P buffer and O may be touched once its previous P V is done
+        if (it > 0) {
+          mbar_wait_bounded(&sm.pv_done[g], (it - 1) & 1u, abort_flag, p.status);
           tc_fence_after();
         }
-        if (r == 0) PF_TRACE(4, it, 0);
-        if (rescale && tile > 0) {
+        if (rescale && have_o) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t orow[32];
-            tmem_ld32(lane_base + 128 + c * 32, orow);
+            tmem_ld32(o_col + c * 32, orow);
             tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
-            tmem_st32(lane_base + 128 + c * 32, orow);
+            tmem_st32(o_col + c * 32, orow);
           }
           tmem_wait_st();
         }
 #pragma unroll
         for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(sm.p + swz128(r, c)) =
+          *reinterpret_cast<uint4*>(p_buf + swz128(r, c)) =
               make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
-        if (r == 0) PF_TRACE(5, it, 0);
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive(&sm.p_full);
-        if (r == 0) PF_TRACE(6, it, 0);
+        mbar_arrive(&sm.p_full[g]);
+        if (r == 0) PF_TRACE(3 + g * 10, it);
+        have_o = true;
       }
-      // ---- epilogue: O / l -> global
+      if (r == 0 && g == 0) PF_TRACE(7, it > 0 ? it - 1 : 0);
+      // ---- merge the two groups and write the item: group g writes columns [64 g, 64 g + 64)
+      sm.row_m[g][r] = have_o ? m_used : -INFINITY;
+      sm.row_l[g][r] = have_o ? l : 0.f;
       mbar_wait_bounded(&sm.o_done, item_no & 1u, abort_flag, p.status);
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      named_bar_sync(1, kTcSoftmaxThreads);
       {
+        const float ma = sm.row_m[0][r], mb = sm.row_m[1][r];
+        const float mm = fmaxf(ma, mb);
+        const float fa = (ma == -INFINITY) ? 0.f : fast_exp2((ma - mm) * p.scale_log2);
+        const float fb = (mb == -INFINITY) ? 0.f : fast_exp2((mb - mm) * p.scale_log2);
+        const float lsum = sm.row_l[0][r] * fa + sm.row_l[1][r] * fb;
+        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+        const float wa = fa * inv, wb = fb * inv;
+        const bool use_a = ma != -INFINITY, use_b = mb != -INFINITY;   // warp-uniform? no: per row
+        const bool any_a = __any_sync(0xffffffffu, use_a), any_b = __any_sync(0xffffffffu, use_b);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t orow[32];
-          if (item.n_tiles > 0) {
-            tmem_ld32(lane_base + 128 + c * 32, orow);
-            tmem_wait_ld();
-          } else {                       // no visible key at all: the row reads as an empty part
+        for (int c = 0; c < 2; ++c) {
+          const int col = g * 64 + c * 32;
+          uint32_t oa[32], ob[32];
+          if (any_a) tmem_ld32(lane_base + 256 + col, oa);
+          if (any_b) tmem_ld32(lane_base + 384 + col, ob);
+          tmem_wait_ld();
+          float res[32];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) orow[i] = 0u;
+          for (int i = 0; i < 32; ++i) {
+            const float xa = use_a ? __uint_as_float(oa[i]) * wa : 0.f;   // never multiply unwritten TMEM
+            const float xb = use_b ? __uint_as_float(ob[i]) * wb : 0.f;
+            res[i] = xa + xb;
           }
           if (valid) {
-            const int64_t off = (tok * p.num_q_heads + head) * kPfHeadDim + c * 32;
+            const int64_t off = (tok * p.num_q_heads + head) * kPfHeadDim + col;
             if (p.out_is_f32) {
               float* dst = reinterpret_cast<float*>(p.out) + off;
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<float4*>(dst + i) =
-                    make_float4(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv,
-                                __uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
+                *reinterpret_cast<float4*>(dst + i) = make_float4(res[i], res[i + 1], res[i + 2], res[i + 3]);
             } else {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {
                 uint4 v;
-                v.x = pack_bf16(__uint_as_float(orow[i]) * inv, __uint_as_float(orow[i + 1]) * inv);
-                v.y = pack_bf16(__uint_as_float(orow[i + 2]) * inv, __uint_as_float(orow[i + 3]) * inv);
-                v.z = pack_bf16(__uint_as_float(orow[i + 4]) * inv, __uint_as_float(orow[i + 5]) * inv);
-                v.w = pack_bf16(__uint_as_float(orow[i + 6]) * inv, __uint_as_float(orow[i + 7]) * inv);
+                v.x = pack_bf16(res[i], res[i + 1]);
+                v.y = pack_bf16(res[i + 2], res[i + 3]);
+                v.z = pack_bf16(res[i + 4], res[i + 5]);
+                v.w = pack_bf16(res[i + 6], res[i + 7]);
                 *reinterpret_cast<uint4*>(dst + i) = v;
               }
             }
           }
         }
+        if (valid && p.lse_out && g == 0)
+          p.lse_out[tok * p.num_q_heads + head] = lsum > 0.f ? mm * p.scale + __logf(lsum) : -INFINITY;
       }
-      if (valid && p.lse_out)
-        p.lse_out[tok * p.num_q_heads + head] = l > 0.f ? m_used * p.scale + __logf(l) : -INFINITY;
+      // nobody may start the next item (new Q, new P V into O) while the other
+      // group still reads this item's accumulators or row state
       tc_fence_before();
+      named_bar_sync(1, kTcSoftmaxThreads);
+      if (r == 0 && g == 0) PF_TRACE(8, it > 0 ? it - 1 : 0);
     }
   }
   // ---- teardown: everyone is done with tensor memory before it is released
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, kTcTmemCols);
   }
@@ -515,7 +559,7 @@ extern "C" int b200_prefill_plan(const int32_t* cu_q, const int32_t* kv_lens,
     for (int row0 = 0; row0 < rows; row0 += kPfRows) {
       const int last_row = std::min(row0 + kPfRows, rows) - 1;
       const int lim = std::min(base + last_row / group, kv_lens[b] - 1);   // last visible key of the item
-      const int n_tiles = lim < 0 ? 0 : lim / kTileTokens + 1;
+      const int n_tiles = lim < 0 ? 0 : lim / kPfTile + 1;
       for (int h = 0; h < num_kv_heads; ++h) {
         items.push_back(PrefillItem{b, h, row0, n_tiles, kv_lens[b], q_start, q_len, base});
         total_tiles += n_tiles;
@@ -536,6 +580,7 @@ extern "C" int b200_prefill_plan(const int32_t* cu_q, const int32_t* kv_lens,
   info->reserved = 0;
   return B200_OK;
 }
+
 
 #ifdef B200_TRACE
 static long long* g_pf_trace = nullptr;
@@ -572,7 +617,7 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
     set_last_error("paged_prefill_gqa: q must be 4-byte aligned with an even stride >= Hq*D, out 16-byte aligned");
     return B200_EALIGN;
   }
-  const int box_tokens = block_size < kTileTokens ? block_size : kTileTokens;
+  const int box_tokens = block_size < 64 ? block_size : 64;
   CUtensorMap k_map, v_map;
   int rc = get_cache_tensor_map(key_cache, num_blocks, block_size, num_kv_heads, head_dim, box_tokens, &k_map);
   if (rc) return rc;
@@ -596,7 +641,7 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   p.block_shift = __builtin_ctz(block_size);
   p.num_blocks = num_blocks;
   p.box_tokens = box_tokens;
-  p.boxes_per_tile = kTileTokens / box_tokens;
+  p.boxes_per_tile = kPfTile / box_tokens;
   p.out_is_f32 = out_is_f32;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;

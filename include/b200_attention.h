@@ -146,7 +146,7 @@ int b200_paged_decode_gqa(const void* q, int64_t q_stride,
  * share it do not overlap on the GPU. */
 typedef struct b200_prefill_plan_info {
   int32_t num_items;       /* 128-row work items                               */
-  int32_t total_tiles;     /* 64-token KV tiles summed over the items          */
+  int32_t total_tiles;     /* 128-token KV tiles summed over the items          */
   int32_t plan_ints;       /* int32 words of the plan actually used            */
   int32_t reserved;
 } b200_prefill_plan_info;
