@@ -123,6 +123,33 @@ class ContextParallelDecode:
         self.out = torch.empty(self.num_tokens, num_q_heads, head_dim, dtype=torch.bfloat16,
                                device=device)
 
+    def capture(self, q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                local_block_table: torch.Tensor, scale: float, before=None):
+        """Record one layer-step (optional ``before`` callable, e.g. the slot write,
+        then local attention, all-gather and merge) into a CUDA graph over the
+        given fixed-address tensors and return it; ``graph.replay()`` then runs
+        the step without per-kernel host launches.  The step runs eagerly a few
+        times first so that every lazy initialisation (kernel attributes, tensor
+        maps, NCCL channels) happens outside the capture.  All ranks of the group
+        must call this together."""
+        def step():
+            if before is not None:
+                before()
+            return self.attend(q, key_cache, value_cache, local_block_table, scale)
+
+        side = torch.cuda.Stream(device=q.device)
+        side.wait_stream(torch.cuda.current_stream(q.device))
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                step()
+        torch.cuda.current_stream(q.device).wait_stream(side)
+        torch.cuda.synchronize(q.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+        torch.cuda.synchronize(q.device)
+        return graph
+
     def attend(self, q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                local_block_table: torch.Tensor, scale: float) -> torch.Tensor:
         """One layer-step: local attention -> all-gather -> merge.  Returns the

@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--no-side-configs", action="store_true",
                     help="skip the kernel-only timings of the smaller configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch the step's kernels one by one instead of replaying a CUDA graph")
     return ap.parse_args()
 
 
@@ -336,9 +338,21 @@ def main():
     assert cpd.local_kv == b.seqlens_kv
     owner_of_new_token = (rank == world - 1)        # the rank holding position context-1
 
-    def step():
+    def write_new_token():
         if owner_of_new_token:
             ops.reshape_and_cache(b.k_new, b.v_new, k_cache, v_cache, b.slot_mapping)
+
+    # the layer-step (slot write, attention, all-gather, merge) is recorded once into a
+    # CUDA graph and replayed: the engine's graph mode does the same for whole decode steps
+    graph = None
+    if not args.no_graph:
+        graph = cpd.capture(b.q, k_cache, v_cache, b.block_table, b.scale, before=write_new_token)
+
+    def step():
+        if graph is not None:
+            graph.replay()
+            return cpd.out
+        write_new_token()
         return cpd.attend(b.q, k_cache, v_cache, b.block_table, b.scale)
 
     def barrier():
@@ -481,7 +495,13 @@ def main():
             line["other_configs"] = side
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Tear down in dependency order: a CUDA graph that recorded NCCL kernels has to go
+        # before its communicator, and the exit must not wait on peers that already left.
+        graph = None
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
