@@ -327,6 +327,11 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        # NCCL prints its version banner to stdout at VERSION/INFO level; rank 0's stdout must
+        # carry the JSON line only
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE") and \
+                not os.environ.get("B200_BENCH_KEEP_NCCL_DEBUG"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     # ---- workload: this rank's slice of every sequence's pages -------------
