@@ -24,6 +24,36 @@ int get_cache_tensor_map(const void* cache, int num_blocks, int block_size, int 
 // ---- device ---------------------------------------------------------------
 #ifdef __CUDACC__
 
+// Launch with programmatic stream serialisation: the kernel may be scheduled
+// while its predecessor in the stream is still draining, and synchronises with
+// it itself through grid_dep_wait().  Saves the launch latency between the
+// back-to-back kernels of a layer-step (slot write -> attention -> merge).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// Blocks until every kernel this one depends on has completed and its writes are
+// visible (no-op when the kernel was launched the ordinary way).
+__device__ __forceinline__ void grid_dep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets the next kernel of the stream be scheduled from now on.
+__device__ __forceinline__ void grid_dep_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

@@ -10,6 +10,7 @@ __global__ void __launch_bounds__(256)
 lse_combine_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
                    int64_t stride_o, int64_t stride_lse, int n_parts, int64_t rows, int dim,
                    void* __restrict__ out, int out_is_f32, float* __restrict__ lse_out) {
+  grid_dep_wait();                // the parts come from the kernel (or collective) before this one
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -59,8 +60,8 @@ extern "C" int b200_lse_combine(const float* o_parts, const float* lse_parts, in
   }
   const int warps = 8;
   const int64_t blocks = (rows + warps - 1) / warps;
-  lse_combine_kernel<<<(unsigned)blocks, warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      o_parts, lse_parts, part_stride_o, part_stride_lse, n_parts, rows, head_dim, out, out_is_f32,
-      lse_out);
-  return check_cuda(cudaGetLastError(), "lse_combine launch");
+  return check_cuda(launch_pdl(lse_combine_kernel, dim3((unsigned)blocks), dim3(warps * 32), 0,
+                               static_cast<cudaStream_t>(stream), o_parts, lse_parts, part_stride_o,
+                               part_stride_lse, n_parts, rows, head_dim, out, out_is_f32, lse_out),
+                    "lse_combine launch");
 }

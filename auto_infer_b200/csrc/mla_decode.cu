@@ -107,6 +107,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
     mbar_fence_init();
   }
   __syncthreads();
+  grid_dep_launch();              // the merge kernel may be scheduled; it waits for this grid itself
+  grid_dep_wait();                // q and the step's new latent rows come from earlier kernels
   if (item_begin >= item_end) return;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -502,13 +504,14 @@ extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
     if (rc) return rc;
     if (dev < 64) attr_set[dev] = true;
   }
-  mla_decode_kernel<<<info->num_ctas, kMlaThreads, smem, s>>>(lat_map, p);
-  rc = check_cuda(cudaGetLastError(), "mla_decode launch");
+  rc = check_cuda(launch_pdl(mla_decode_kernel, dim3(info->num_ctas), dim3(kMlaThreads), smem, s, lat_map, p),
+                  "mla_decode launch");
   if (rc) return rc;
   if (info->num_multi > 0) {
-    split_merge_kernel<kValueDim><<<split_merge_grid<kValueDim>(info->num_multi), 128, 0, s>>>(
-        plan_dev, p.part_o, p.part_lse, out, lse_out, num_heads, num_heads, out_is_f32);
-    rc = check_cuda(cudaGetLastError(), "mla_merge launch");
+    rc = check_cuda(launch_pdl(split_merge_kernel<kValueDim>, dim3(split_merge_grid<kValueDim>(info->num_multi)),
+                               dim3(128), 0, s, plan_dev, (const float*)p.part_o, (const float*)p.part_lse,
+                               out, lse_out, num_heads, num_heads, out_is_f32),
+                    "mla_merge launch");
   }
   return rc;
 }

@@ -115,6 +115,8 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     mbar_fence_init();
   }
   __syncthreads();
+  grid_dep_launch();              // the merge kernel may be scheduled; it waits for this grid itself
+  grid_dep_wait();                // q and the step's new cache rows come from earlier kernels
   if (item_begin >= item_end) return;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -528,13 +530,15 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
     if (rc) return rc;
     if (dev < 64) attr_set[dev] = true;
   }
-  paged_decode_gqa_kernel<<<info->num_ctas, kDecodeThreads, smem, s>>>(k_map, v_map, p);
-  rc = check_cuda(cudaGetLastError(), "paged_decode_gqa launch");
+  rc = check_cuda(launch_pdl(paged_decode_gqa_kernel, dim3(info->num_ctas), dim3(kDecodeThreads), smem, s,
+                             k_map, v_map, p),
+                  "paged_decode_gqa launch");
   if (rc) return rc;
   if (info->num_multi > 0) {
-    split_merge_kernel<kHeadDim><<<split_merge_grid<kHeadDim>(info->num_multi), 128, 0, s>>>(
-        plan_dev, p.part_o, p.part_lse, out, lse_out, num_q_heads, p.group, out_is_f32);
-    rc = check_cuda(cudaGetLastError(), "decode_merge launch");
+    rc = check_cuda(launch_pdl(split_merge_kernel<kHeadDim>, dim3(split_merge_grid<kHeadDim>(info->num_multi)),
+                               dim3(128), 0, s, plan_dev, (const float*)p.part_o, (const float*)p.part_lse,
+                               out, lse_out, num_q_heads, p.group, out_is_f32),
+                    "decode_merge launch");
   }
   return rc;
 }

@@ -157,6 +157,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dep_wait();                // q and the step's new cache rows come from earlier kernels
   const uint32_t tmem = sm.tmem_base;
   volatile int* abort_flag = &sm.abort_flag;
   // Items are handed out dynamically, longest first: the producer warp draws the
@@ -663,6 +664,8 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   int grid = b200_sm_count();
   if (grid <= 0) grid = 148;
   if (grid > info->num_items) grid = info->num_items;
-  paged_prefill_tc_kernel<<<grid, kTcThreads, smem_tc, static_cast<cudaStream_t>(stream)>>>(k_map, v_map, p);
+  return check_cuda(launch_pdl(paged_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), smem_tc,
+                               static_cast<cudaStream_t>(stream), k_map, v_map, p),
+                    "paged_prefill_gqa launch");
   return check_cuda(cudaGetLastError(), "paged_prefill_gqa launch");
 }

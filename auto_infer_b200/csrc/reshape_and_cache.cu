@@ -13,6 +13,8 @@ reshape_and_cache_kernel(const Vec* __restrict__ key, const Vec* __restrict__ va
                          const int32_t* __restrict__ slot_mapping, int64_t key_stride,
                          int64_t value_stride, int k_row, int v_row, int64_t total_slots,
                          int32_t* status) {
+  grid_dep_launch();              // the attention kernel may set itself up while rows are copied
+  grid_dep_wait();                // the rows come from the kernel before this one
   const int t = blockIdx.x;
   const int64_t slot = slot_mapping[t];
   if (slot < 0) return;  // padding row
@@ -63,13 +65,17 @@ extern "C" int b200_reshape_and_cache(const void* key, const void* value, void* 
   if (vec) {
     const int row16 = (int)(k_row / 8);
     const int threads = row16 >= 256 ? 256 : (row16 >= 128 ? 128 : 64);
-    reshape_and_cache_kernel<uint4><<<num_tokens, threads, 0, s>>>(
-        (const uint4*)key, (const uint4*)value, (uint4*)key_cache, (uint4*)value_cache, slot_mapping,
-        key_stride / 8, value_stride / 8, (int)(k_row / 8), (int)(v_row / 8), total_slots, status);
-  } else {
-    reshape_and_cache_kernel<uint16_t><<<num_tokens, 256, 0, s>>>(
-        (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)key_cache, (uint16_t*)value_cache,
-        slot_mapping, key_stride, value_stride, (int)k_row, (int)v_row, total_slots, status);
+    return check_cuda(
+        launch_pdl(reshape_and_cache_kernel<uint4>, dim3(num_tokens), dim3(threads), 0, s,
+                   (const uint4*)key, (const uint4*)value, (uint4*)key_cache, (uint4*)value_cache,
+                   slot_mapping, key_stride / 8, value_stride / 8, (int)(k_row / 8), (int)(v_row / 8),
+                   total_slots, status),
+        "reshape_and_cache launch");
   }
-  return check_cuda(cudaGetLastError(), "reshape_and_cache launch");
+  return check_cuda(
+      launch_pdl(reshape_and_cache_kernel<uint16_t>, dim3(num_tokens), dim3(256), 0, s,
+                 (const uint16_t*)key, (const uint16_t*)value, (uint16_t*)key_cache,
+                 (uint16_t*)value_cache, slot_mapping, key_stride, value_stride, (int)k_row, (int)v_row,
+                 total_slots, status),
+      "reshape_and_cache launch");
 }
