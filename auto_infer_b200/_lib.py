@@ -65,6 +65,10 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, POINTER(DecodePlanInfo), c_int, c_int, c_int, c_float,
         c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_cp_exchange_buffer_bytes": (c_size_t, [c_int, c_int64, c_int]),
+    "b200_cp_exchange_combine": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int,
+        c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_lse_combine": (c_int, [
         c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int,
         c_void_p, c_int, c_void_p, c_void_p]),

@@ -23,6 +23,7 @@ SOURCES = [
     "paged_prefill_gqa.cu",
     "mla_decode.cu",
     "lse_combine.cu",
+    "cp_exchange.cu",
 ]
 
 NVCC_FLAGS = [

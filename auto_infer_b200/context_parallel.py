@@ -99,6 +99,29 @@ def split_gathered(gathered: torch.Tensor, rows: int, head_dim: int):
     return o, lse
 
 
+class PeerExchange:
+    """Symmetric receive buffers for the fused exchange + merge kernel: one buffer
+    per rank, mapped into every peer of the group (torch symmetric memory does
+    the handle exchange), plus this rank's step counter.  Collective: all ranks
+    of the group construct it together."""
+
+    def __init__(self, rows: int, head_dim: int, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        from . import _lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.rows, self.head_dim = rows, head_dim
+        nbytes = _lib.load().b200_cp_exchange_buffer_bytes(self.world, rows, head_dim)
+        self.buffer = symm_mem.empty(nbytes // 4, dtype=torch.float32, device=device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        self.buffer.zero_()
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)          # every flag word is zero before anyone pushes
+        self.recv_ptrs_dev = int(self.handle.buffer_ptrs_dev)
+
+
 class ContextParallelDecode:
     """Holds the per-step plan and buffers of one CP rank and runs a layer-step."""
 
@@ -161,6 +184,12 @@ class ContextParallelDecode:
             self.partial.clear()
         ops.paged_decode_gqa(q, key_cache, value_cache, local_block_table, self.meta.decode, scale,
                              out=self.partial.o, lse_out=self.partial.lse)
+        if self.exchange is not None:
+            # one kernel: peer-to-peer push of [o | lse], flag wait, merge
+            ops.cp_exchange_combine(self.partial.flat, self.exchange.recv_ptrs_dev, self.exchange.state,
+                                    self.cp_rank, self.cp_size, self.partial.rows, self.partial.head_dim,
+                                    self.out.view(self.partial.rows, -1))
+            return self.out
         gathered = all_gather_partials(self.partial.flat, self.group)
         o_parts, lse_parts = split_gathered(gathered, self.partial.rows, self.partial.head_dim)
         ops.lse_combine(o_parts, lse_parts, out=self.out.view(self.partial.rows, -1))

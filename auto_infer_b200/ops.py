@@ -325,3 +325,22 @@ def lse_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor,
             lse_out.data_ptr() if lse_out is not None else None, _stream_ptr(o_parts.device))
     _lib.check(rc, "b200_lse_combine")
     return out
+
+
+def cp_exchange_combine(local_record: torch.Tensor, recv_ptrs_dev: int, state: torch.Tensor, rank: int,
+                        world: int, rows: int, head_dim: int, out: torch.Tensor,
+                        lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused context-parallel exchange + merge: push this rank's packed fp32
+    record [o | lse] to every rank's receive buffer over NVLink, wait for all
+    ranks' records and merge them into ``out`` (rows, head_dim).  ``recv_ptrs_dev``
+    is the device address of the array of receive-buffer pointers."""
+    _need_cuda(local_record, state, out)
+    lib = _lib.load()
+    with torch.cuda.device(local_record.device):
+        rc = lib.b200_cp_exchange_combine(
+            local_record.data_ptr(), recv_ptrs_dev, state.data_ptr(), rank, world, rows, head_dim,
+            out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+            lse_out.data_ptr() if lse_out is not None else None,
+            status_word(local_record.device).data_ptr(), _stream_ptr(local_record.device))
+    _lib.check(rc, "b200_cp_exchange_combine")
+    return out

@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--no-side-configs", action="store_true",
                     help="skip the kernel-only timings of the smaller configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "p2p", "nccl"],
+                    help="context-parallel exchange: fused peer-to-peer kernel or NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step's kernels one by one instead of replaying a CUDA graph")
     return ap.parse_args()
@@ -338,8 +340,20 @@ def main():
     b = synth.config5(device, cp_rank=rank, cp_size=world, context=args.context, batch=args.batch)
     k_cache, v_cache = b.kv_cache[0], b.kv_cache[1]
     global_kv = [args.context] * args.batch
+    exchange, exchange_kind = None, "none"
+    if world > 1:
+        exchange_kind = "nccl all-gather + merge kernel"
+        if args.exchange != "nccl":
+            try:
+                from auto_infer_b200.context_parallel import PeerExchange
+                exchange = PeerExchange(args.batch * b.n_q, b.head_dim, device)
+                exchange_kind = "fused peer-to-peer push + merge kernel"
+            except Exception as exc:          # no symmetric memory on this box: keep the NCCL exchange
+                if args.exchange == "p2p":
+                    raise
+                print(f"peer exchange unavailable ({exc!r}); using NCCL", file=sys.stderr)
     cpd = ContextParallelDecode(b.cu_seqlens_q, global_kv, b.n_q, b.n_kv, b.head_dim, b.block_size,
-                                device, cp_rank=rank, cp_size=world)
+                                device, cp_rank=rank, cp_size=world, exchange=exchange)
     assert cpd.local_kv == b.seqlens_kv
     owner_of_new_token = (rank == world - 1)        # the rank holding position context-1
 
@@ -429,7 +443,8 @@ def main():
             o = backend.paged_attention(0, dev["q"], dev["k_new"], dev["v_new"], ctx)
         else:
             plan = ContextParallelDecode(b.cu_seqlens_q, global_kv, b.n_q, b.n_kv, b.head_dim,
-                                         b.block_size, device, cp_rank=rank, cp_size=world)
+                                         b.block_size, device, cp_rank=rank, cp_size=world,
+                                         exchange=exchange)
             if owner_of_new_token:
                 ops.reshape_and_cache(dev["k_new"], dev["v_new"], k_cache, v_cache, dev["slot_mapping"])
             o = plan.attend(dev["q"], k_cache, v_cache, dev["block_table"], b.scale)

@@ -41,7 +41,7 @@ def test_emulated_ranks_merge_to_the_unsplit_answer(ranks):
     assert ops.read_status("cuda") == 0
 
 
-def _nccl_worker(rank, world, port, ret):
+def _nccl_worker(rank, world, port, ret, use_p2p=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -52,12 +52,16 @@ def _nccl_worker(rank, world, port, ret):
         b = synth.build_gqa_batch("cp", [(1, 3000), (2, 700), (1, 130)], 16, 8, 128, 40, 23)
         d = b.to(f"cuda:{rank}")
         local_bt = cp.shard_block_table(d.block_table, b.seqlens_kv, 128, rank, world)
+        exchange = cp.PeerExchange(b.num_tokens * b.n_q, b.head_dim, f"cuda:{rank}") if use_p2p else None
         step = cp.ContextParallelDecode(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, 128,
-                                        f"cuda:{rank}", cp_rank=rank, cp_size=world)
-        out = step.attend(d.q, d.kv_cache[0], d.kv_cache[1], local_bt, b.scale)
+                                        f"cuda:{rank}", cp_rank=rank, cp_size=world, exchange=exchange)
         ref = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
                                   b.seqlens_kv, b.scale)
-        torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL)
+        for _ in range(3):            # several steps: the step counter and both slots are exercised
+            out = step.attend(d.q, d.kv_cache[0], d.kv_cache[1], local_bt, b.scale)
+            torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL)
+        from auto_infer_b200 import ops
+        assert ops.read_status(f"cuda:{rank}") == 0
         ret[rank] = "ok"
     finally:
         dist.destroy_process_group()
@@ -72,4 +76,17 @@ def test_two_gpu_nccl_all_gather_and_merge():
     with mp.Manager() as mgr:
         ret = mgr.dict()
         mp.spawn(_nccl_worker, args=(2, port, ret), nprocs=2, join=True)
+        assert dict(ret) == {0: "ok", 1: "ok"}
+
+
+@pytest.mark.timeout(300)
+def test_two_gpu_fused_peer_exchange_and_merge():
+    """Same answer through the fused peer-to-peer exchange + merge kernel."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    port = 29700 + os.getpid() % 2000
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_nccl_worker, args=(2, port, ret, True), nprocs=2, join=True)
         assert dict(ret) == {0: "ok", 1: "ok"}
