@@ -127,8 +127,10 @@ class ContextParallelDecode:
 
     def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv_global: Sequence[int],
                  num_q_heads: int, num_kv_heads: int, head_dim: int, block_size: int, device,
-                 group=None, cp_rank: Optional[int] = None, cp_size: Optional[int] = None):
+                 group=None, cp_rank: Optional[int] = None, cp_size: Optional[int] = None,
+                 exchange: Optional["PeerExchange"] = None):
         self.group = group
+        self.exchange = exchange          # None: NCCL all-gather + merge kernel
         if cp_size is None:
             cp_size = dist.get_world_size(group) if dist.is_initialized() else 1
         if cp_rank is None:
