@@ -498,7 +498,7 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "us_per_layer_step": ms_per_step * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic", "config": workload_config(args, world),
+            "data": "synthetic", "config": dict(workload_config(args, world), exchange=exchange_kind),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
                          "kernel": "paged_decode_gqa_kernel (+ decode_merge_kernel, one C call)",
