@@ -139,18 +139,23 @@ static int build_split_plan(const char* who, int tile_tokens, const int32_t* cu_
         it.causal_base = base;
         it.direct = (take == tiles) ? 1 : 0;
         it.partial_idx = it.direct ? -1 : n_parts++;
-        it.pad0 = it.pad1 = 0;
+        it.multi_idx = -1;
+        it.pad1 = 0;
         t += take;
         cap -= take;
       }
       if (n_parts > first_part) {
+        // the items of this pair are the last ones emitted: point them at the pair's record
+        for (int k = n_items - 1; k >= 0 && items[k].seq == b && items[k].kv_head == h; --k)
+          items[k].multi_idx = n_multi;
         MultiGroup& g = multi[n_multi++];
         g.q_start = q_start;
         g.q_len = q_len;
         g.kv_head = h;
         g.part_begin = first_part;
         g.part_end = n_parts;
-        g.pad0 = g.pad1 = g.pad2 = 0;
+        g.arrivals = 0;
+        g.pad1 = g.pad2 = 0;
       }
     }
   }

@@ -22,13 +22,16 @@ enum PlanHeader {
 struct DecodeItem {
   int32_t seq, kv_head, tile_begin, tile_end;
   int32_t kv_len, q_start, q_len, causal_base;   // key j visible to row i iff j <= causal_base + i
-  int32_t partial_idx, direct, pad0, pad1;       // direct: item covers the whole pair, write final output
+  int32_t partial_idx, direct, multi_idx, pad1;  // direct: item covers the whole pair, write final output;
+                                                 // multi_idx: the pair's MultiGroup record when it is cut
 };
 static_assert(sizeof(DecodeItem) == kItemInts * 4, "item layout");
 
 // A (sequence, kv head) pair split over several items; merged by the combine pass.
 struct MultiGroup {
-  int32_t q_start, q_len, kv_head, part_begin, part_end, pad0, pad1, pad2;
+  int32_t q_start, q_len, kv_head, part_begin, part_end;
+  int32_t arrivals;    // device-side: items of the pair that have written their record (GQA decode merges in-kernel)
+  int32_t pad1, pad2;
 };
 static_assert(sizeof(MultiGroup) == kMultiInts * 4, "group layout");
 

@@ -14,12 +14,12 @@
 //   * at the end of an item the eight warps merge their (m, l, O) through shared
 //     memory in a fixed order (deterministic) and write either the final bf16
 //     rows (the item covered the whole pair) or one fp32 partial (o, lse).
-// A second small kernel (split_merge.cuh) merges the partials of pairs that were cut.
+// The partials of a pair that was cut are merged by the CTA whose record arrives
+// last (an arrival counter per pair in the plan), so the step needs no second kernel.
 //
 // Algorithmic bytes per launch: sum_b kv_len_b * 2 * Hkv * 128 * 2 B (+ q, o).
 #include "common.cuh"
 #include "decode_plan.h"
-#include "split_merge.cuh"
 
 namespace b200 {
 
@@ -47,6 +47,7 @@ struct __align__(1024) DecodeSmem {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   int abort_flag;
+  int merge_parts[2];                                        // [part_begin, part_end) when this CTA merges a pair
 };
 
 static_assert(sizeof(DecodeSmem) + 1024 <= 227 * 1024, "shared memory budget of one CTA");
@@ -56,7 +57,7 @@ struct DecodeParams {
   int64_t q_stride;                 // elements between query tokens
   const int32_t* block_table;
   int64_t bt_stride;
-  const int32_t* plan;
+  int32_t* plan;                    // the pairs' arrival counters in it are updated by the kernel
   float* part_o;                    // (num_partials, 16, 128) fp32
   float* part_lse;                  // (num_partials, 16)
   void* out;                        // (T, Hq, 128) bf16 or fp32
@@ -69,6 +70,7 @@ struct DecodeParams {
   int block_size, block_shift, num_blocks;
   int box_tokens, boxes_per_tile;
   int out_is_f32;
+  int off_cta, off_items, off_multi;   // plan offsets (derivable from the grid size and item count)
   float scale, scale_log2;
 };
 
@@ -83,7 +85,7 @@ struct TileWalker {
       int4 a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2);
       cur.seq = a.x; cur.kv_head = a.y; cur.tile_begin = a.z; cur.tile_end = a.w;
       cur.kv_len = b.x; cur.q_start = b.y; cur.q_len = b.z; cur.causal_base = b.w;
-      cur.partial_idx = c.x; cur.direct = c.y;
+      cur.partial_idx = c.x; cur.direct = c.y; cur.multi_idx = c.z;
       tile = cur.tile_begin;
       tile_end = cur.tile_end;
     }
@@ -101,8 +103,8 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   const int lane = threadIdx.x & 31;
 
   const int32_t* plan = p.plan;
-  const int32_t* cta_off = plan + plan[kHdrOffCta];
-  const DecodeItem* items = reinterpret_cast<const DecodeItem*>(plan + plan[kHdrOffItems]);
+  const int32_t* cta_off = plan + p.off_cta;
+  const DecodeItem* items = reinterpret_cast<const DecodeItem*>(plan + p.off_items);
   const int item_begin = cta_off[blockIdx.x];
   const int item_end = cta_off[blockIdx.x + 1];
 
@@ -115,7 +117,7 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     mbar_fence_init();
   }
   __syncthreads();
-  grid_dep_launch();              // the merge kernel may be scheduled; it waits for this grid itself
+  grid_dep_launch();              // the next kernel may be scheduled; it waits for this grid itself
   grid_dep_wait();                // q and the step's new cache rows come from earlier kernels
   if (item_begin >= item_end) return;
   volatile int* abort_flag = &sm.abort_flag;
@@ -430,6 +432,57 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
           if ((t & 15) == 0) p.part_lse[(int64_t)item.partial_idx * kMaxRows + row] = lse;
         }
       }
+      // ---- a cut pair is merged by the CTA whose record arrives last: no second kernel
+      if (!item.direct) {
+        __threadfence();                                   // my part of the record is visible device-wide
+        named_bar_sync(1, kConsumerThreads);
+        if (t == 0) {
+          MultiGroup* mg = reinterpret_cast<MultiGroup*>(p.plan + p.off_multi) + item.multi_idx;
+          const int n_parts = mg->part_end - mg->part_begin;
+          const bool last = atomicAdd(&mg->arrivals, 1) == n_parts - 1;
+          if (last) {
+            mg->arrivals = 0;                              // ready for the next launch on this plan
+            __threadfence();
+          }
+          sm.merge_parts[0] = last ? mg->part_begin : 0;
+          sm.merge_parts[1] = last ? mg->part_end : 0;
+        }
+        named_bar_sync(1, kConsumerThreads);
+        const int pb = sm.merge_parts[0], pe = sm.merge_parts[1];
+        if (pe > pb && row < rows) {
+          float mx = -INFINITY;
+          for (int pi = pb; pi < pe; ++pi) mx = fmaxf(mx, __ldcg(p.part_lse + (int64_t)pi * kMaxRows + row));
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          float wsum = 0.f;
+#pragma unroll 4
+          for (int pi = pb; pi < pe; ++pi) {
+            const float l = __ldcg(p.part_lse + (int64_t)pi * kMaxRows + row);
+            const float wgt = (l == -INFINITY) ? 0.f : __expf(l - mx);
+            const float4* src = reinterpret_cast<const float4*>(
+                p.part_o + ((int64_t)pi * kMaxRows + row) * kHeadDim + col);
+            const float4 a = __ldcg(src), b2 = __ldcg(src + 1);
+            wsum += wgt;
+            acc[0] += wgt * a.x; acc[1] += wgt * a.y; acc[2] += wgt * a.z; acc[3] += wgt * a.w;
+            acc[4] += wgt * b2.x; acc[5] += wgt * b2.y; acc[6] += wgt * b2.z; acc[7] += wgt * b2.w;
+          }
+          const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+          const int64_t tok = item.q_start + row / G;
+          const int head = item.kv_head * G + row % G;
+          const int64_t off = (tok * p.num_q_heads + head) * kHeadDim + col;
+          if (p.out_is_f32) {
+            float* dst = reinterpret_cast<float*>(p.out) + off;
+            *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+          } else {
+            uint4 pk;
+            pk.x = pack_bf16(acc[0] * inv, acc[1] * inv); pk.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+            pk.z = pack_bf16(acc[4] * inv, acc[5] * inv); pk.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pk;
+          }
+          if (p.lse_out && (t & 15) == 0)
+            p.lse_out[tok * p.num_q_heads + head] = wsum > 0.f ? mx + __logf(wsum) : -INFINITY;
+        }
+      }
     }
     // the next item's first shared-memory write of the merge area comes after
     // its own first barrier, which no thread passes before finishing the reads above
@@ -448,7 +501,7 @@ extern "C" void b200_debug_set_trace(void* host_mapped) { g_trace = static_cast<
 extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void* key_cache,
                                      const void* value_cache, int num_blocks, int block_size,
                                      const int32_t* block_table, int64_t bt_stride,
-                                     const int32_t* plan_dev, const b200_decode_plan_info* info,
+                                     int32_t* plan_dev, const b200_decode_plan_info* info,
                                      int num_q_heads, int num_kv_heads, int head_dim, float scale,
                                      void* workspace, size_t workspace_bytes, void* out,
                                      int out_is_f32, float* lse_out, int32_t* status,
@@ -498,6 +551,9 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
   p.block_table = block_table;
   p.bt_stride = bt_stride;
   p.plan = plan_dev;
+  p.off_cta = kPlanHeaderInts;
+  p.off_items = p.off_cta + round_up4(info->num_ctas + 1);
+  p.off_multi = p.off_items + kItemInts * info->num_items;
   p.part_o = static_cast<float*>(workspace);
   p.part_lse = p.part_o + (size_t)info->num_partials * kMaxRows * kHeadDim;
   p.out = out;
@@ -534,12 +590,6 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
                              k_map, v_map, p),
                   "paged_decode_gqa launch");
   if (rc) return rc;
-  if (info->num_multi > 0) {
-    rc = check_cuda(launch_pdl(split_merge_kernel<kHeadDim>, dim3(split_merge_grid<kHeadDim>(info->num_multi)),
-                               dim3(128), 0, s, plan_dev, (const float*)p.part_o, (const float*)p.part_lse,
-                               out, lse_out, num_q_heads, p.group, out_is_f32),
-                    "decode_merge launch");
-  }
   return rc;
 }
 
@@ -562,7 +612,7 @@ static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
 extern "C" int b200_paged_decode_gqa_static(const void* q, int64_t q_stride, const void* key_cache,
                                             const void* value_cache, int num_blocks, int block_size,
                                             const int32_t* block_table, int64_t bt_stride,
-                                            const int32_t* plan_dev,
+                                            int32_t* plan_dev,
                                             const b200_decode_plan_info* info, int num_q_heads,
                                             int num_kv_heads, int head_dim, float scale, void* out,
                                             int out_is_f32, float* lse_out, int32_t* status,

@@ -115,7 +115,10 @@ int b200_decode_plan(const int32_t* cu_seqlens_q_host, const int32_t* seqlens_kv
  *   q (T, Hq, 128) bf16, row stride q_stride elements
  *   caches (num_blocks, block_size, Hkv, 128) bf16; block_size a power of two >= 8
  *   block_table (B, >= blocks needed) int32, row stride bt_stride
- *   plan_dev: device copy of the plan built by b200_decode_plan (info by value)
+ *   plan_dev: device copy of the plan built by b200_decode_plan; not const: it holds one
+ *             arrival counter per cut pair that the kernel counts up and puts back to zero,
+ *             so one plan serves all layers of a step as long as calls sharing it do not
+ *             overlap on the GPU
  *   workspace: b200_decode_workspace_bytes() bytes, 256-byte aligned
  *   out: (T, Hq, 128) bf16 when out_is_f32 == 0, fp32 otherwise (the fp32 form
  *        is one context-parallel rank's partial); lse_out (T, Hq) fp32 or NULL
@@ -124,7 +127,7 @@ int b200_paged_decode_gqa(const void* q, int64_t q_stride,
                           const void* key_cache, const void* value_cache,
                           int num_blocks, int block_size,
                           const int32_t* block_table, int64_t bt_stride,
-                          const int32_t* plan_dev, const b200_decode_plan_info* info,
+                          int32_t* plan_dev, const b200_decode_plan_info* info,
                           int num_q_heads, int num_kv_heads, int head_dim, float scale,
                           void* workspace, size_t workspace_bytes,
                           void* out, int out_is_f32, float* lse_out,
@@ -196,7 +199,7 @@ int b200_paged_decode_gqa_static(const void* q, int64_t q_stride,
                                  const void* key_cache, const void* value_cache,
                                  int num_blocks, int block_size,
                                  const int32_t* block_table, int64_t bt_stride,
-                                 const int32_t* plan_dev, const b200_decode_plan_info* info,
+                                 int32_t* plan_dev, const b200_decode_plan_info* info,
                                  int num_q_heads, int num_kv_heads, int head_dim, float scale,
                                  void* out, int out_is_f32, float* lse_out,
                                  int32_t* status, void* stream);
