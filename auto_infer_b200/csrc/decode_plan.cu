@@ -98,8 +98,23 @@ static int build_split_plan(const char* who, int tile_tokens, const int32_t* cu_
   int32_t* cta_off = plan + off_cta;
   DecodeItem* items = reinterpret_cast<DecodeItem*>(plan + off_items);
 
-  const int64_t quota_lo = total / num_ctas;
-  const int rem = (int)(total % num_ctas);
+  // Every item costs its tiles plus a fixed overhead (merge of the warps' partial
+  // states, the record or output write, the next Q): ranges are cut to equal COST, so
+  // a CTA whose range crosses pair boundaries gets fewer tiles.  The number of items
+  // is about pairs + CTAs; any rounding error only shortens the last ranges.
+  int64_t pairs = 0;
+  {
+    int pv = 0;
+    for (int b = 0; b < num_seqs; ++b) {
+      const int q_len = cu_q[b] - pv;
+      pv = cu_q[b];
+      if (q_len > 0 && kv_lens[b] > 0 && q_len * group <= kMaxRows) pairs += num_kv_heads;
+    }
+  }
+  const int64_t item_cost = total >= 8 * (int64_t)num_ctas ? kItemOverheadTiles : 0;   // tiny steps: pure tile balance
+  const int64_t total_cost = total + item_cost * (pairs + num_ctas);
+  const int64_t quota_lo = total_cost / num_ctas;
+  const int rem = (int)(total_cost % num_ctas);
   auto quota = [&](int c) -> int64_t { return quota_lo + (c < rem ? 1 : 0); };
 
   int n_items = 0, n_parts = 0, n_multi = 0;
@@ -122,12 +137,14 @@ static int build_split_plan(const char* who, int tile_tokens, const int32_t* cu_
       int t = 0;
       int first_part = n_parts;
       while (t < tiles) {
-        while (cap == 0) {  // advance to the next CTA that still has room
+        while (cap <= item_cost && cta + 1 < num_ctas) {  // no room for an item plus a tile: next CTA
           ++cta;
           cta_off[cta] = n_items;
           cap = quota(cta);
         }
-        const int take = (int)((tiles - t) < cap ? (tiles - t) : cap);
+        int64_t room = cap - item_cost;
+        if (room < 1 || cta + 1 == num_ctas) room = tiles - t;       // the last CTA takes what is left
+        const int take = (int)((tiles - t) < room ? (tiles - t) : room);
         DecodeItem& it = items[n_items++];
         it.seq = b;
         it.kv_head = h;
@@ -142,7 +159,7 @@ static int build_split_plan(const char* who, int tile_tokens, const int32_t* cu_
         it.multi_idx = -1;
         it.pad1 = 0;
         t += take;
-        cap -= take;
+        cap -= take + item_cost;
       }
       if (n_parts > first_part) {
         // the items of this pair are the last ones emitted: point them at the pair's record

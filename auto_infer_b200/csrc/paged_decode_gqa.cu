@@ -14,12 +14,15 @@
 //   * at the end of an item the eight warps merge their (m, l, O) through shared
 //     memory in a fixed order (deterministic) and write either the final bf16
 //     rows (the item covered the whole pair) or one fp32 partial (o, lse).
-// The partials of a pair that was cut are merged by the CTA whose record arrives
-// last (an arrival counter per pair in the plan), so the step needs no second kernel.
+// A second small kernel (split_merge.cuh, launched with programmatic dependent
+// launch) merges the partials of pairs that were cut; merging inside this kernel
+// by the last-arriving CTA was tried and put the merge's dependent L2 loads on the
+// consumers' critical path for no gain.
 //
 // Algorithmic bytes per launch: sum_b kv_len_b * 2 * Hkv * 128 * 2 B (+ q, o).
 #include "common.cuh"
 #include "decode_plan.h"
+#include "split_merge.cuh"
 
 namespace b200 {
 
@@ -47,7 +50,6 @@ struct __align__(1024) DecodeSmem {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   int abort_flag;
-  int merge_parts[2];                                        // [part_begin, part_end) when this CTA merges a pair
 };
 
 static_assert(sizeof(DecodeSmem) + 1024 <= 227 * 1024, "shared memory budget of one CTA");
@@ -64,7 +66,7 @@ struct DecodeParams {
   float* lse_out;                   // (T, Hq) or null
   int32_t* status;
 #ifdef B200_TRACE
-  volatile int* trace;              // host-mapped progress records, 32 ints per CTA (debug builds)
+  long long* trace;                 // %globaltimer samples, 16 per CTA (debug builds)
 #endif
   int num_q_heads, num_kv_heads, group;
   int block_size, block_shift, num_blocks;
@@ -117,8 +119,14 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     mbar_fence_init();
   }
   __syncthreads();
+#ifdef B200_TRACE
+  if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 0] = (long long)global_timer_ns();
+#endif
   grid_dep_launch();              // the next kernel may be scheduled; it waits for this grid itself
   grid_dep_wait();                // q and the step's new cache rows come from earlier kernels
+#ifdef B200_TRACE
+  if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 1] = (long long)global_timer_ns();
+#endif
   if (item_begin >= item_end) return;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -169,12 +177,7 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
         uint8_t* dst = sm.stage[s] + lane * p.box_tokens * 128;
         const int h = w.cur.kv_head;
 #ifdef B200_TRACE
-        if (p.trace && lane == 0) {
-          volatile int* tr = p.trace + blockIdx.x * 32;
-          tr[1] = h; tr[2] = tok; tr[3] = b; tr[4] = s; tr[5] = w.item; tr[6] = w.tile;
-          tr[0] = (int)it + 1;
-          __threadfence_system();
-        }
+        if (p.trace && lane == 0 && it == 0) p.trace[blockIdx.x * 16 + 2] = (long long)global_timer_ns();
 #endif
         tma_load_4d(dst, &k_map, &sm.full[s], 0, h, tok, b);
         tma_load_4d(dst + kHalfTileBytes, &k_map, &sm.full[s], 64, h, tok, b);
@@ -214,30 +217,33 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   w.load();
   uint32_t it = 0;
 
+  // Q fragments of an item: 8 k-steps x 4 registers, rows beyond q_len*group are zero.
+  // They are fetched for the NEXT item right after the tile loop, so the global
+  // loads fly while the warps merge and write the current item.
+  uint32_t qf[8][4];
+  auto load_q = [&](const DecodeItem& qi) {
+    const int qrows = qi.q_len * G;
+    const int r0 = quad, r1 = quad + 8;
+    const __nv_bfloat16* q0 = nullptr;
+    const __nv_bfloat16* q1 = nullptr;
+    if (r0 < qrows)
+      q0 = p.q + (int64_t)(qi.q_start + r0 / G) * p.q_stride + (int64_t)(qi.kv_head * G + r0 % G) * kHeadDim;
+    if (r1 < qrows)
+      q1 = p.q + (int64_t)(qi.q_start + r1 / G) * p.q_stride + (int64_t)(qi.kv_head * G + r1 % G) * kHeadDim;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int c = ks * 16 + qlane * 2;
+      qf[ks][0] = q0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + c)) : 0u;
+      qf[ks][1] = q1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + c)) : 0u;
+      qf[ks][2] = q0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + c + 8)) : 0u;
+      qf[ks][3] = q1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + c + 8)) : 0u;
+    }
+  };
+  load_q(w.cur);
+
   while (w.item < w.item_end) {
     const DecodeItem item = w.cur;
     const int rows = item.q_len * G;
-    // ---- Q fragments: 8 k-steps x 4 registers, rows beyond q_len*group are zero
-    uint32_t qf[8][4];
-    {
-      const int r0 = quad, r1 = quad + 8;
-      const __nv_bfloat16* q0 = nullptr;
-      const __nv_bfloat16* q1 = nullptr;
-      if (r0 < rows)
-        q0 = p.q + (int64_t)(item.q_start + r0 / G) * p.q_stride +
-             (int64_t)(item.kv_head * G + r0 % G) * kHeadDim;
-      if (r1 < rows)
-        q1 = p.q + (int64_t)(item.q_start + r1 / G) * p.q_stride +
-             (int64_t)(item.kv_head * G + r1 % G) * kHeadDim;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const int c = ks * 16 + qlane * 2;
-        qf[ks][0] = q0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + c)) : 0u;
-        qf[ks][1] = q1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + c)) : 0u;
-        qf[ks][2] = q0 ? __ldg(reinterpret_cast<const uint32_t*>(q0 + c + 8)) : 0u;
-        qf[ks][3] = q1 ? __ldg(reinterpret_cast<const uint32_t*>(q1 + c + 8)) : 0u;
-      }
-    }
     // last visible key per fragment row (-1: row unused, everything masked)
     const int lim0 = quad < rows ? min(item.causal_base + quad / G, item.kv_len - 1) : -1;
     const int lim1 = quad + 8 < rows ? min(item.causal_base + (quad + 8) / G, item.kv_len - 1) : -1;
@@ -326,14 +332,18 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.empty[s]);
 #ifdef B200_TRACE
-      if (p.trace && lane == 0) {
-        p.trace[blockIdx.x * 32 + 8 + warp] = (int)it + 1;
-        __threadfence_system();
+      if (p.trace && lane == 0 && warp < 2) {
+        if (it < 2) p.trace[blockIdx.x * 16 + 3 + warp * 4] = (long long)global_timer_ns();   // first tile done
+        p.trace[blockIdx.x * 16 + 4 + warp * 4] = (long long)global_timer_ns();               // latest tile done
+        p.trace[blockIdx.x * 16 + 6] = it + 1;
       }
 #endif
     }
 
-    // ---- merge the eight warps (fixed order) and write the item's result
+    // ---- next item's Q on its way, then merge the eight warps (fixed order) and write the result
+    ++w.item;
+    w.load();
+    if (w.item < w.item_end) load_q(w.cur);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -432,70 +442,20 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
           if ((t & 15) == 0) p.part_lse[(int64_t)item.partial_idx * kMaxRows + row] = lse;
         }
       }
-      // ---- a cut pair is merged by the CTA whose record arrives last: no second kernel
-      if (!item.direct) {
-        __threadfence();                                   // my part of the record is visible device-wide
-        named_bar_sync(1, kConsumerThreads);
-        if (t == 0) {
-          MultiGroup* mg = reinterpret_cast<MultiGroup*>(p.plan + p.off_multi) + item.multi_idx;
-          const int n_parts = mg->part_end - mg->part_begin;
-          const bool last = atomicAdd(&mg->arrivals, 1) == n_parts - 1;
-          if (last) {
-            mg->arrivals = 0;                              // ready for the next launch on this plan
-            __threadfence();
-          }
-          sm.merge_parts[0] = last ? mg->part_begin : 0;
-          sm.merge_parts[1] = last ? mg->part_end : 0;
-        }
-        named_bar_sync(1, kConsumerThreads);
-        const int pb = sm.merge_parts[0], pe = sm.merge_parts[1];
-        if (pe > pb && row < rows) {
-          float mx = -INFINITY;
-          for (int pi = pb; pi < pe; ++pi) mx = fmaxf(mx, __ldcg(p.part_lse + (int64_t)pi * kMaxRows + row));
-          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          float wsum = 0.f;
-#pragma unroll 4
-          for (int pi = pb; pi < pe; ++pi) {
-            const float l = __ldcg(p.part_lse + (int64_t)pi * kMaxRows + row);
-            const float wgt = (l == -INFINITY) ? 0.f : __expf(l - mx);
-            const float4* src = reinterpret_cast<const float4*>(
-                p.part_o + ((int64_t)pi * kMaxRows + row) * kHeadDim + col);
-            const float4 a = __ldcg(src), b2 = __ldcg(src + 1);
-            wsum += wgt;
-            acc[0] += wgt * a.x; acc[1] += wgt * a.y; acc[2] += wgt * a.z; acc[3] += wgt * a.w;
-            acc[4] += wgt * b2.x; acc[5] += wgt * b2.y; acc[6] += wgt * b2.z; acc[7] += wgt * b2.w;
-          }
-          const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-          const int64_t tok = item.q_start + row / G;
-          const int head = item.kv_head * G + row % G;
-          const int64_t off = (tok * p.num_q_heads + head) * kHeadDim + col;
-          if (p.out_is_f32) {
-            float* dst = reinterpret_cast<float*>(p.out) + off;
-            *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
-          } else {
-            uint4 pk;
-            pk.x = pack_bf16(acc[0] * inv, acc[1] * inv); pk.y = pack_bf16(acc[2] * inv, acc[3] * inv);
-            pk.z = pack_bf16(acc[4] * inv, acc[5] * inv); pk.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pk;
-          }
-          if (p.lse_out && (t & 15) == 0)
-            p.lse_out[tok * p.num_q_heads + head] = wsum > 0.f ? mx + __logf(wsum) : -INFINITY;
-        }
-      }
     }
+#ifdef B200_TRACE
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 5] = (long long)global_timer_ns();   // item written
+#endif
     // the next item's first shared-memory write of the merge area comes after
     // its own first barrier, which no thread passes before finishing the reads above
-    ++w.item;
-    w.load();
   }
 }
 
 }  // namespace b200
 
 #ifdef B200_TRACE
-static volatile int* g_trace = nullptr;
-extern "C" void b200_debug_set_trace(void* host_mapped) { g_trace = static_cast<volatile int*>(host_mapped); }
+static long long* g_trace = nullptr;
+extern "C" void b200_debug_set_trace(void* dev_ptr) { g_trace = static_cast<long long*>(dev_ptr); }
 #endif
 
 extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void* key_cache,
@@ -590,6 +550,12 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
                              k_map, v_map, p),
                   "paged_decode_gqa launch");
   if (rc) return rc;
+  if (info->num_multi > 0) {
+    rc = check_cuda(launch_pdl(split_merge_kernel<kHeadDim>, dim3(split_merge_grid<kHeadDim>(info->num_multi)),
+                               dim3(128), 0, s, (const int32_t*)plan_dev, (const float*)p.part_o,
+                               (const float*)p.part_lse, out, lse_out, num_q_heads, p.group, out_is_f32),
+                    "decode_merge launch");
+  }
   return rc;
 }
 
