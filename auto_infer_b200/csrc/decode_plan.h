@@ -6,7 +6,7 @@ namespace b200 {
 
 constexpr int kTileTokens = 64;      // KV tokens per pipeline stage (GQA kernels)
 constexpr int kMlaTileTokens = 32;   // latent tokens per pipeline stage (MLA decode)
-constexpr int kItemOverheadTiles = 3;   // planner's cost of one work item, in tiles
+constexpr int kItemOverheadTiles = 5;   // planner's cost of one work item, in tiles
 constexpr int kMaxRows = 16;         // q_len * group rows one MMA tile holds
 constexpr int kPlanMagic = 0x62323030;
 constexpr int kPlanHeaderInts = 16;

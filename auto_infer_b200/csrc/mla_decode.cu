@@ -9,12 +9,14 @@
 //   * producer warp: nine 4 KB TMA boxes (64 dims x 32 tokens, 128-byte swizzle)
 //     per tile into a 4-stage ring (36 KB per stage);
 //   * two consumer groups of four warps take alternate tiles (even ring: a stage
-//     always belongs to one group).  Inside a group, warps 0-1 compute
-//     S = Q K^T for 16 tokens each over all 576 dims (q_len*heads <= 16 rows form
-//     the M of mma.sync m16n8k16; Q fragments come from shared memory), the
-//     group agrees on the row maxima through shared memory, P goes to shared
-//     memory as bf16, and all four warps accumulate O += P V for 128 of the 512
-//     value dims each;
+//     always belongs to one group).  Inside a group every warp computes a
+//     quarter of S = Q K^T (16 of the tile's 32 tokens x half of the 576 dims;
+//     q_len*heads <= 16 rows form the M of mma.sync m16n8k16, Q fragments come
+//     from shared memory), the four partial score blocks meet in shared memory
+//     behind ONE barrier per tile, every warp then holds the full 16 x 32 scores
+//     in MMA-fragment layout, runs the same online softmax (identical row state
+//     in all four warps, nothing else to exchange) and accumulates O += P V for
+//     its 128 of the 512 value dims with P straight from registers;
 //   * the groups' (m, l, O) are merged in a fixed order at the end of an item.
 // Algorithmic bytes per launch: sum_b kv_len_b * 1 152 B (+ q, o).
 #include "common.cuh"
@@ -34,14 +36,12 @@ constexpr int kMlaWarps = 8;
 constexpr int kMlaConsumerThreads = kMlaWarps * 32;
 constexpr int kMlaThreads = kMlaConsumerThreads + 32;
 constexpr int kQPitch = kLatentDim * 2 + 16;                  // bytes per Q row in shared memory
-constexpr int kPPitch = kMlaTileTokens * 2 + 16;              // bytes per P row in shared memory
 
 struct __align__(1024) MlaSmem {
   uint8_t stage[kMlaStages][kMlaStageBytes];
   float slots[4][kMaxRows * 128];                             // merge buffer: one 128-dim slice per warp pair
   __align__(16) uint8_t qbuf[kMaxRows * kQPitch];
-  __align__(16) uint8_t pbuf[2][kMaxRows * kPPitch];
-  float m_part[2][2][kMaxRows];
+  float s_part[2][2][4][32 * 8];                              // [group][tile parity][warp][lane x 8] partial scores
   float red_m[2][kMaxRows];
   float red_l[kMlaWarps][kMaxRows];
   uint64_t full[kMlaStages];
@@ -179,7 +179,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   const int gbar = 1 + grp;            // named barrier of the group (128 threads)
 
   // ldmatrix lane addressing
-  const int k_tok = gw * 16 + ((lane >> 4) << 3) + (lane & 7);        // K operand (S warps only)
+  const int slice = gw & 1;            // 16-token slice of the tile this warp scores
+  const int khalf = gw >> 1;           // latent sub-tiles [0,5) or [5,9)
+  const int k_tok = slice * 16 + ((lane >> 4) << 3) + (lane & 7);     // K operand
   const int k_chunk_sel = (lane >> 3) & 1;
   const int v_tok_l = (((lane >> 3) & 1) << 3) + (lane & 7);          // V operand
   const int v_chunk_sel = lane >> 4;
@@ -214,7 +216,6 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
     for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
     const uint32_t qbase = smem_u32(sm.qbuf) + a_row * kQPitch + a_koff * 2;
-    const uint32_t pbase = smem_u32(sm.pbuf[grp]) + a_row * kPPitch + a_koff * 2;
 
     for (int tile = item.tile_begin; tile < item.tile_end; ++tile, ++it) {
       if ((int)(it & 1u) != grp) continue;
@@ -222,58 +223,65 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
       mbar_wait_bounded(&sm.full[s], (it / kMlaStages) & 1u, abort_flag, p.status);
       const uint32_t sbase = smem_u32(sm.stage[s]);
 
-      float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      if (gw < 2) {
-        // ---- S = Q K^T for this warp's 16 tokens over 576 dims; four independent
-        // accumulator sets (one per k-step of a 64-dim sub-tile) keep the
-        // dependent mma chain at 9 instead of 36
-        float part[4][2][4];
+      // ---- this warp's quarter of S = Q K^T: 16 tokens x sub-tiles [sub0, sub1); two
+      // accumulator sets per n-tile keep the dependent mma chain short
+      float part[2][2][4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < 2; ++u)
 #pragma unroll
-          for (int n = 0; n < 2; ++n) part[u][n][0] = part[u][n][1] = part[u][n][2] = part[u][n][3] = 0.f;
-#pragma unroll 3
-        for (int sub = 0; sub < kMlaSub; ++sub) {
+        for (int n = 0; n < 2; ++n) part[u][n][0] = part[u][n][1] = part[u][n][2] = part[u][n][3] = 0.f;
+      const int sub0 = khalf ? 5 : 0, sub1 = khalf ? kMlaSub : 5;
+#pragma unroll 1
+      for (int sub = sub0; sub < sub1; ++sub) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint32_t qa[4], kb[4];
-            ldmatrix_x4(qa, qbase + (sub * 4 + u) * 32);
-            ldmatrix_x4(kb, sbase + sub * kMlaSubBytes + swz128(k_tok, u * 2 + k_chunk_sel));
-            mma_bf16_16816(part[u][0], qa, kb[0], kb[1]);
-            mma_bf16_16816(part[u][1], qa, kb[2], kb[3]);
-          }
+        for (int u = 0; u < 4; ++u) {
+          uint32_t qa[4], kb[4];
+          ldmatrix_x4(qa, qbase + (sub * 4 + u) * 32);
+          ldmatrix_x4(kb, sbase + sub * kMlaSubBytes + swz128(k_tok, u * 2 + k_chunk_sel));
+          mma_bf16_16816(part[u & 1][0], qa, kb[0], kb[1]);
+          mma_bf16_16816(part[u & 1][1], qa, kb[2], kb[3]);
         }
+      }
+      float* my_part = sm.s_part[grp][(it >> 1) & 1][gw] + lane * 8;
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+        *reinterpret_cast<float4*>(my_part + n * 4) =
+            make_float4(part[0][n][0] + part[1][n][0], part[0][n][1] + part[1][n][1],
+                        part[0][n][2] + part[1][n][2], part[0][n][3] + part[1][n][3]);
+      named_bar_sync(gbar, 128);
+      // ---- full scores of the tile in fragment layout: sacc[kt][n] = tokens kt*16 + n*8 ...
+      float sacc[2][2][4];
+      {
+        const float (*pp)[32 * 8] = sm.s_part[grp][(it >> 1) & 1];
+#pragma unroll
+        for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+          for (int n = 0; n < 2; ++n) {
+            const float4 a = *reinterpret_cast<const float4*>(pp[kt] + lane * 8 + n * 4);       // dims [0,320)
+            const float4 c = *reinterpret_cast<const float4*>(pp[kt + 2] + lane * 8 + n * 4);   // dims [320,576)
+            sacc[kt][n][0] = a.x + c.x; sacc[kt][n][1] = a.y + c.y;
+            sacc[kt][n][2] = a.z + c.z; sacc[kt][n][3] = a.w + c.w;
+          }
+      }
+      const int tok0 = tile * kMlaTileTokens + qlane * 2;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt)
 #pragma unroll
         for (int n = 0; n < 2; ++n)
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            sacc[n][e] = (part[0][n][e] + part[1][n][e]) + (part[2][n][e] + part[3][n][e]);
-        const int tok0 = tile * kMlaTileTokens + gw * 16 + qlane * 2;
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-#pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int j = tok0 + n * 8 + e;
-            if (j > lim0) sacc[n][e] = -INFINITY;
-            if (j > lim1) sacc[n][2 + e] = -INFINITY;
-            mx0 = fmaxf(mx0, sacc[n][e]);
-            mx1 = fmaxf(mx1, sacc[n][2 + e]);
+            const int j = tok0 + kt * 16 + n * 8 + e;
+            if (j > lim0) sacc[kt][n][e] = -INFINITY;
+            if (j > lim1) sacc[kt][n][2 + e] = -INFINITY;
+            mx0 = fmaxf(mx0, sacc[kt][n][e]);
+            mx1 = fmaxf(mx1, sacc[kt][n][2 + e]);
           }
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        if (qlane == 0) {
-          sm.m_part[grp][gw][quad] = mx0;
-          sm.m_part[grp][gw][quad + 8] = mx1;
-        }
-      }
-      named_bar_sync(gbar, 128);
-      // ---- group-wide row maxima, correction of the running state
-      const float mn0 = fmaxf(m0, fmaxf(sm.m_part[grp][0][quad], sm.m_part[grp][1][quad]));
-      const float mn1 = fmaxf(m1, fmaxf(sm.m_part[grp][0][quad + 8], sm.m_part[grp][1][quad + 8]));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
       const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0 * p.scale_log2;
       const float ms1 = (mn1 == -INFINITY) ? 0.f : mn1 * p.scale_log2;
       if (__any_sync(0xffffffffu, (mn0 != m0) || (mn1 != m1))) {
@@ -288,27 +296,28 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
         m0 = mn0;
         m1 = mn1;
       }
-      if (gw < 2) {
-        // ---- P (bf16) to shared memory, row-major [16][32 tokens]
+      uint32_t pf[2][4];
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        float pr[2][4];
 #pragma unroll
         for (int n = 0; n < 2; ++n) {
-          const float p0 = fast_exp2(fmaf(sacc[n][0], p.scale_log2, -ms0));
-          const float p1 = fast_exp2(fmaf(sacc[n][1], p.scale_log2, -ms0));
-          const float p2 = fast_exp2(fmaf(sacc[n][2], p.scale_log2, -ms1));
-          const float p3 = fast_exp2(fmaf(sacc[n][3], p.scale_log2, -ms1));
-          l0 += p0 + p1;
-          l1 += p2 + p3;
-          const int col = gw * 16 + n * 8 + qlane * 2;
-          *reinterpret_cast<uint32_t*>(sm.pbuf[grp] + quad * kPPitch + col * 2) = pack_bf16(p0, p1);
-          *reinterpret_cast<uint32_t*>(sm.pbuf[grp] + (quad + 8) * kPPitch + col * 2) = pack_bf16(p2, p3);
+          pr[n][0] = fast_exp2(fmaf(sacc[kt][n][0], p.scale_log2, -ms0));
+          pr[n][1] = fast_exp2(fmaf(sacc[kt][n][1], p.scale_log2, -ms0));
+          pr[n][2] = fast_exp2(fmaf(sacc[kt][n][2], p.scale_log2, -ms1));
+          pr[n][3] = fast_exp2(fmaf(sacc[kt][n][3], p.scale_log2, -ms1));
+          l0 += pr[n][0] + pr[n][1];
+          l1 += pr[n][2] + pr[n][3];
         }
+        pf[kt][0] = pack_bf16(pr[0][0], pr[0][1]);
+        pf[kt][1] = pack_bf16(pr[0][2], pr[0][3]);
+        pf[kt][2] = pack_bf16(pr[1][0], pr[1][1]);
+        pf[kt][3] = pack_bf16(pr[1][2], pr[1][3]);
       }
-      named_bar_sync(gbar, 128);
       // ---- O[:, 128*gw .. +128) += P V over the tile's 32 tokens
 #pragma unroll
       for (int kt = 0; kt < 2; ++kt) {
-        uint32_t pa[4];
-        ldmatrix_x4(pa, pbase + kt * 32);
+        const uint32_t (&pa)[4] = pf[kt];
         const int tok = kt * 16 + v_tok_l;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -334,8 +343,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
         sm.red_m[grp][quad] = m0;
         sm.red_m[grp][quad + 8] = m1;
       }
-      sm.red_l[warp][quad] = l0;           // zero for the warps that computed no S
-      sm.red_l[warp][quad + 8] = l1;
+      sm.red_l[warp][quad] = (gw == 0) ? l0 : 0.f;   // all four warps of a group hold the same row sums
+      sm.red_l[warp][quad + 8] = (gw == 0) ? l1 : 0.f;
     }
     named_bar_sync(3, kMlaConsumerThreads);
     const float ga0 = fmaxf(sm.red_m[0][quad], sm.red_m[1][quad]);
