@@ -65,7 +65,19 @@ struct MlaParams {
   int block_size, block_shift, num_blocks, box_tokens, boxes_per_tile;
   int out_is_f32;
   float scale, scale_log2;
+#ifdef B200_TRACE
+  long long* trace;                // clock samples of CTA 0, 8 per tile (debug builds)
+#endif
 };
+
+#ifdef B200_TRACE
+#define MLA_TRACE(slot, tileno)                                                                  \
+  do {                                                                                           \
+    if (p.trace && blockIdx.x == 0 && lane == 0 && (tileno) < 64) p.trace[(tileno) * 8 + (slot)] = clock64(); \
+  } while (0)
+#else
+#define MLA_TRACE(slot, tileno) do {} while (0)
+#endif
 
 struct MlaWalker {
   const DecodeItem* items;
@@ -140,6 +152,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
       if (lane == 0) {
         mbar_wait_bounded(&sm.empty[s], ((it / kMlaStages) & 1u) ^ 1u, abort_flag, p.status);
         mbar_arrive_expect_tx(&sm.full[s], kMlaStageBytes);
+        MLA_TRACE(6, it);
       }
       __syncwarp();
       // box i of the tile by lane i; each lane issues its nine 64-dim slices
@@ -196,16 +209,27 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   while (w.item < w.item_end) {
     const DecodeItem item = w.cur;
     const int rows = item.q_len * G;
-    // ---- stage Q (rows x 576, zero padded to 16 rows) in shared memory
-    for (int i = threadIdx.x; i < kMaxRows * (kLatentDim / 8); i += kMlaConsumerThreads) {
-      const int r = i / (kLatentDim / 8), c = i % (kLatentDim / 8);
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (r < rows) {
-        const __nv_bfloat16* src = p.q + (int64_t)(item.q_start + r / G) * p.q_stride +
-                                   (int64_t)(r % G) * kLatentDim + c * 8;
-        v = __ldg(reinterpret_cast<const uint4*>(src));
+    // ---- stage Q (rows x 576, zero padded to 16 rows) in shared memory: all loads of a
+    // thread are issued before its first store, so their latencies overlap
+    {
+      constexpr int kChunks = kMaxRows * (kLatentDim / 8);              // 16-byte chunks
+      constexpr int kPerThread = (kChunks + kMlaConsumerThreads - 1) / kMlaConsumerThreads;
+      uint4 qv[kPerThread];
+#pragma unroll
+      for (int u = 0; u < kPerThread; ++u) {
+        const int i = threadIdx.x + u * kMlaConsumerThreads;
+        const int r = i / (kLatentDim / 8), c = i % (kLatentDim / 8);
+        qv[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < kChunks && r < rows)
+          qv[u] = __ldg(reinterpret_cast<const uint4*>(p.q + (int64_t)(item.q_start + r / G) * p.q_stride +
+                                                       (int64_t)(r % G) * kLatentDim + c * 8));
       }
-      *reinterpret_cast<uint4*>(sm.qbuf + r * kQPitch + c * 16) = v;
+#pragma unroll
+      for (int u = 0; u < kPerThread; ++u) {
+        const int i = threadIdx.x + u * kMlaConsumerThreads;
+        if (i < kChunks)
+          *reinterpret_cast<uint4*>(sm.qbuf + (i / (kLatentDim / 8)) * kQPitch + (i % (kLatentDim / 8)) * 16) = qv[u];
+      }
     }
     named_bar_sync(3, kMlaConsumerThreads);
 
@@ -220,7 +244,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
     for (int tile = item.tile_begin; tile < item.tile_end; ++tile, ++it) {
       if ((int)(it & 1u) != grp) continue;
       const int s = it % kMlaStages;
+      if (gw == 0) MLA_TRACE(0, it);
       mbar_wait_bounded(&sm.full[s], (it / kMlaStages) & 1u, abort_flag, p.status);
+      if (gw == 0) MLA_TRACE(1, it);
       const uint32_t sbase = smem_u32(sm.stage[s]);
 
       // ---- this warp's quarter of S = Q K^T: 16 tokens x sub-tiles [sub0, sub1); two
@@ -230,16 +256,25 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
       for (int u = 0; u < 2; ++u)
 #pragma unroll
         for (int n = 0; n < 2; ++n) part[u][n][0] = part[u][n][1] = part[u][n][2] = part[u][n][3] = 0.f;
-      const int sub0 = khalf ? 5 : 0, sub1 = khalf ? kMlaSub : 5;
-#pragma unroll 1
-      for (int sub = sub0; sub < sub1; ++sub) {
+      // sub-tiles [0,5) or [5,9), 4 k-steps each.  The inline-asm loads and MMAs keep
+      // program order, so the operand loads are software-pipelined by hand: the fragments
+      // of k-step st+2 are requested before the MMAs of k-step st are issued.
+      const int sub0 = khalf ? 5 : 0;
+      const int nsteps = (khalf ? kMlaSub - 5 : 5) * 4;
+      uint32_t qa[3][4], kb[3][4];
+      auto load_step = [&](int st, int buf) {
+        const int sub = sub0 + (st >> 2), u = st & 3;
+        ldmatrix_x4(qa[buf], qbase + (sub * 4 + u) * 32);
+        ldmatrix_x4(kb[buf], sbase + sub * kMlaSubBytes + swz128(k_tok, u * 2 + k_chunk_sel));
+      };
+      load_step(0, 0);
+      load_step(1, 1);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint32_t qa[4], kb[4];
-          ldmatrix_x4(qa, qbase + (sub * 4 + u) * 32);
-          ldmatrix_x4(kb, sbase + sub * kMlaSubBytes + swz128(k_tok, u * 2 + k_chunk_sel));
-          mma_bf16_16816(part[u & 1][0], qa, kb[0], kb[1]);
-          mma_bf16_16816(part[u & 1][1], qa, kb[2], kb[3]);
+      for (int st = 0; st < 20; ++st) {
+        if (st < nsteps) {
+          if (st + 2 < nsteps) load_step(st + 2, (st + 2) % 3);
+          mma_bf16_16816(part[st & 1][0], qa[st % 3], kb[st % 3][0], kb[st % 3][1]);
+          mma_bf16_16816(part[st & 1][1], qa[st % 3], kb[st % 3][2], kb[st % 3][3]);
         }
       }
       float* my_part = sm.s_part[grp][(it >> 1) & 1][gw] + lane * 8;
@@ -248,7 +283,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
         *reinterpret_cast<float4*>(my_part + n * 4) =
             make_float4(part[0][n][0] + part[1][n][0], part[0][n][1] + part[1][n][1],
                         part[0][n][2] + part[1][n][2], part[0][n][3] + part[1][n][3]);
+      if (gw == 0) MLA_TRACE(2, it);
       named_bar_sync(gbar, 128);
+      if (gw == 0) MLA_TRACE(3, it);
       // ---- full scores of the tile in fragment layout: sacc[kt][n] = tokens kt*16 + n*8 ...
       float sacc[2][2][4];
       {
@@ -314,23 +351,31 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
         pf[kt][2] = pack_bf16(pr[1][0], pr[1][1]);
         pf[kt][3] = pack_bf16(pr[1][2], pr[1][3]);
       }
+      if (gw == 0) MLA_TRACE(4, it);
       // ---- O[:, 128*gw .. +128) += P V over the tile's 32 tokens
-#pragma unroll
-      for (int kt = 0; kt < 2; ++kt) {
-        const uint32_t (&pa)[4] = pf[kt];
-        const int tok = kt * 16 + v_tok_l;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
+      {
+        // 16 V fragments (2 token halves x 8 dim pairs), loads two steps ahead of the MMAs
+        uint32_t vb[3][4];
+        auto load_v = [&](int st, int buf) {
+          const int kt = st >> 3, j = st & 7;
+          const int tok = kt * 16 + v_tok_l;
           const int chunk = (j & 3) * 2 + v_chunk_sel;
           const int sub = gw * 2 + (j >> 2);
-          uint32_t vb[4];
-          ldmatrix_x4_trans(vb, sbase + sub * kMlaSubBytes + swz128(tok, chunk));
-          mma_bf16_16816(o[2 * j], pa, vb[0], vb[1]);
-          mma_bf16_16816(o[2 * j + 1], pa, vb[2], vb[3]);
+          ldmatrix_x4_trans(vb[buf], sbase + sub * kMlaSubBytes + swz128(tok, chunk));
+        };
+        load_v(0, 0);
+        load_v(1, 1);
+#pragma unroll
+        for (int st = 0; st < 16; ++st) {
+          if (st + 2 < 16) load_v(st + 2, (st + 2) % 3);
+          const int kt = st >> 3, j = st & 7;
+          mma_bf16_16816(o[2 * j], pf[kt], vb[st % 3][0], vb[st % 3][1]);
+          mma_bf16_16816(o[2 * j + 1], pf[kt], vb[st % 3][2], vb[st % 3][3]);
         }
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.empty[s]);
+      if (gw == 0) MLA_TRACE(5, it);
     }
 
     // ---- merge the two groups in a fixed order, write the item's result
@@ -432,6 +477,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
 
 }  // namespace b200
 
+#ifdef B200_TRACE
+static long long* g_mla_trace = nullptr;
+extern "C" void b200_debug_set_mla_trace(void* dev_ptr) { g_mla_trace = static_cast<long long*>(dev_ptr); }
+#endif
+
 extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
                                         const void* latent_cache, int num_blocks, int block_size,
                                         const int32_t* block_table, int64_t bt_stride,
@@ -500,6 +550,9 @@ extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
   p.out_is_f32 = out_is_f32;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
+#ifdef B200_TRACE
+  p.trace = g_mla_trace;
+#endif
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = sizeof(MlaSmem) + 1024;
