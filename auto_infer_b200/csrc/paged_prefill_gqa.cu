@@ -89,13 +89,11 @@ constexpr int kTcSoftmaxThreads = 256;
 constexpr int kTcThreads = kTcSoftmaxThreads + 96;
 constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O_A [256,384) O_B [384,512)
 constexpr int kTcQBytes = 2 * kPfRows * 128;
-constexpr int kTcPBytes = kPfRows * 128;
 
 struct __align__(1024) TcSmem {
   uint8_t q[kTcQBytes];                    // [dim half][128 rows][128 B], swizzled
   uint8_t k[kTcKStages][kPfTileBytes];     // [dims 0-63 | dims 64-127], 128 tokens x 128 B each
   uint8_t v[kTcVStages][kPfTileBytes];
-  uint8_t p[2][kTcPBytes];                 // per group: [128 rows][64 tokens x 2 B], swizzled
   float row_m[2][kPfRows];                 // end-of-item exchange of the groups' row state
   float row_l[2][kPfRows];
   uint64_t k_full[kTcKStages];
@@ -140,7 +138,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.s_full[b], 1);
-      mbar_init(&sm.s_empty[b], kTcSoftmaxThreads);
+      mbar_init(&sm.s_empty[b], 1);                // committed by the P V issuer: P aliases S
       mbar_init(&sm.p_full[b], 128);
       mbar_init(&sm.pv_done[b], 1);
       mbar_init(&sm.item_full[b], 1);
@@ -280,9 +278,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     // ------------------------- MMA issuer: O += P V --------------------------
     if (lane == 0) {
       constexpr uint32_t idesc_pv = umma_idesc_bf16(kPfRows, kPfHeadDim, true);
-      const uint64_t dp = umma_desc_sw128(smem_u32(sm.p[0]), 16, 1024);
       const uint64_t dv = umma_desc_sw128(smem_u32(sm.v[0]), kPfHalfTileBytes, 1024);
-      const uint32_t dp_lo = (uint32_t)dp, dp_hi = (uint32_t)(dp >> 32);
       const uint32_t dv_lo = (uint32_t)dv, dv_hi = (uint32_t)(dv >> 32);
       uint32_t it = 0;
       for (uint32_t item_no = 0;; ++item_no) {
@@ -298,20 +294,22 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             mbar_wait_bounded(&sm.p_full[g], it & 1u, abort_flag, p.status);
             tc_fence_after();
             PF_TRACE(5 + g * 4, it);
-            const uint32_t p_lo = dp_lo + (uint32_t)((g * kTcPBytes) >> 4);
+            // P of the group: bf16 pairs in the first 32 columns of the group's half of the S buffer
+            const uint32_t p_tmem = tmem + (it & 1u) * 128 + g * 64;
             const uint32_t vg_lo = v_lo + (uint32_t)((g * 64 * 128) >> 4);   // the group's 64 tokens of the tile
             const uint32_t d_tmem = tmem + 256 + g * 128;
             if (tile == 0)                                  // first tile of the item overwrites
-              umma_bf16_ss_lo<false>(d_tmem, p_lo, dp_hi, vg_lo, dv_hi, idesc_pv);
+              umma_bf16_ts_lo<false>(d_tmem, p_tmem, vg_lo, dv_hi, idesc_pv);
             else
-              umma_bf16_ss_lo<true>(d_tmem, p_lo, dp_hi, vg_lo, dv_hi, idesc_pv);
+              umma_bf16_ts_lo<true>(d_tmem, p_tmem, vg_lo, dv_hi, idesc_pv);
 #pragma unroll
             for (int ks = 1; ks < 4; ++ks)
-              umma_bf16_ss_lo<true>(d_tmem, p_lo + (uint32_t)((ks * 32) >> 4), dp_hi,
-                                    vg_lo + (uint32_t)((ks * 2048) >> 4), dv_hi, idesc_pv);
+              umma_bf16_ts_lo<true>(d_tmem, p_tmem + ks * 8, vg_lo + (uint32_t)((ks * 2048) >> 4), dv_hi,
+                                    idesc_pv);
             umma_commit(&sm.pv_done[g]);
           }
           umma_commit(&sm.v_empty[s]);
+          umma_commit(&sm.s_empty[it & 1u]);                // S buffer (and the P inside it) may be overwritten
           PF_TRACE(6, it);
         }
         umma_commit(&sm.o_done);
@@ -325,7 +323,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t s_col = lane_base + g * 64;       // + 128 * (tile & 1)
     const uint32_t o_col = lane_base + 256 + g * 128;
-    uint8_t* p_buf = sm.p[g];
     const int G = p.group;
     uint32_t it = 0;
     for (uint32_t item_no = 0;; ++item_no) {
@@ -364,8 +361,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         tmem_ld32(s_col + sb * 128, sr[0]);
         tmem_ld32(s_col + sb * 128 + 32, sr[1]);
         tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(&sm.s_empty[sb]);
         const int tbase = tile * kPfTile + g * 64;   // first token of this group's columns
         if (tbase + 63 > lim) {
 #pragma unroll
@@ -408,12 +403,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           }
         l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         if (r == 0) PF_TRACE(2 + g * 10, it);
-        // the group's P buffer and O may be touched once its previous P V is done
-        if (it > 0) {
+        // O may be touched once the group's previous P V is done (rare path)
+        if (rescale && have_o) {
           mbar_wait_bounded(&sm.pv_done[g], (it - 1) & 1u, abort_flag, p.status);
           tc_fence_after();
-        }
-        if (rescale && have_o) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t orow[32];
@@ -425,11 +418,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           }
           tmem_wait_st();
         }
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(p_buf + swz128(r, c)) =
-              make_uint4(pk[c * 4], pk[c * 4 + 1], pk[c * 4 + 2], pk[c * 4 + 3]);
-        fence_proxy_async_smem();
+        // P replaces the first half of the columns this thread has just read
+        tmem_st32(s_col + sb * 128, pk);
+        tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_full[g]);
         if (r == 0) PF_TRACE(3 + g * 10, it);

@@ -88,6 +88,27 @@ __device__ __forceinline__ void umma_bf16_ss_lo(uint32_t tmem_d, uint32_t a_lo, 
         ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc));
   }
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (here the bf16 probabilities, two
+// per 32-bit column, one row per lane) is read from tensor memory.
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_bf16_ts_lo(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo,
+                                                uint32_t b_hi, uint32_t idesc) {
+  if constexpr (kAccumulate) {
+    asm volatile(
+        "{\n\t.reg .b64 db;\n\t.reg .pred p;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc));
+  } else {
+    asm volatile(
+        "{\n\t.reg .b64 db;\n\t.reg .pred p;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc));
+  }
+}
 // The mbarrier receives one arrival when every tcgen05.mma issued so far by this
 // thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
