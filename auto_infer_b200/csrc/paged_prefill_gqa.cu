@@ -91,7 +91,7 @@ constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O_A [256,38
 constexpr int kTcQBytes = 2 * kPfRows * 128;
 
 struct __align__(1024) TcSmem {
-  uint8_t q[kTcQBytes];                    // [dim half][128 rows][128 B], swizzled
+  uint8_t q[2][kTcQBytes];                 // per item parity: [dim half][128 rows][128 B], swizzled
   uint8_t k[kTcKStages][kPfTileBytes];     // [dims 0-63 | dims 64-127], 128 tokens x 128 B each
   uint8_t v[kTcVStages][kPfTileBytes];
   float row_m[2][kPfRows];                 // end-of-item exchange of the groups' row state
@@ -105,7 +105,8 @@ struct __align__(1024) TcSmem {
   uint64_t p_full[2];
   uint64_t pv_done[2];
   uint64_t o_done;
-  uint64_t q_full;
+  uint64_t q_full[2];                      // producer warp -> S issuer: the item's Q tile is staged
+  uint64_t q_empty[2];                     // S issuer -> producer warp: all S MMAs of the item have run
   uint64_t item_full[2];                   // work-queue hand-off: producer warp -> the other roles
   uint64_t item_empty[2];
   int next_item[2];
@@ -145,7 +146,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       mbar_init(&sm.item_empty[b], kTcSoftmaxThreads + 2);   // softmax threads + the two MMA threads
     }
     mbar_init(&sm.o_done, 1);
-    mbar_init(&sm.q_full, kTcSoftmaxThreads);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.q_full[b], 32);
+      mbar_init(&sm.q_empty[b], 1);
+    }
     mbar_fence_init();
   }
   if (warp == 9) {
@@ -188,6 +192,38 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       idx = __shfl_sync(0xffffffffu, idx, 0);
       if (idx < 0) break;
       const PrefillItem item = p.items[idx];
+      // ---- stage the item's Q tile (K-major, 128-byte swizzle, zero for unused rows) in the
+      // buffer of its parity, one item ahead of the MMAs: lane l copies rows l, l+32, ...
+      {
+        const int qb = k & 1u;
+        if (lane == 0) mbar_wait_bounded(&sm.q_empty[qb], ((k >> 1) & 1u) ^ 1u, abort_flag, p.status);
+        __syncwarp();
+        const int rows_total = item.q_len * p.group;
+#pragma unroll 1
+        for (int rr = 0; rr < kPfRows; rr += 64) {
+          uint4 v[2][16];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int r = rr + h * 32 + lane;
+            const int rg = item.row0 + r;
+            const bool valid = rg < rows_total;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                p.q + (int64_t)(item.q_start + (valid ? rg / p.group : 0)) * p.q_stride +
+                (int64_t)(item.kv_head * p.group + (valid ? rg % p.group : 0)) * kPfHeadDim);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) v[h][c] = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int r = rr + h * 32 + lane;
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              *reinterpret_cast<uint4*>(sm.q[qb] + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v[h][c];
+          }
+        }
+        fence_proxy_async_smem();
+        mbar_arrive(&sm.q_full[qb]);
+      }
       const int last_block = (item.kv_len - 1) >> p.block_shift;
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
         int bid = 0;
@@ -241,7 +277,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfRows, kPfTile, false);
       // descriptors differ only in their start-address field: build once, add offsets
-      const uint64_t dq = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
+      const uint64_t dq = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
       const uint64_t dk = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024);
       const uint32_t dq_lo = (uint32_t)dq, dq_hi = (uint32_t)(dq >> 32);
       const uint32_t dk_lo = (uint32_t)dk, dk_hi = (uint32_t)(dk >> 32);
@@ -250,7 +286,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         const int idx = take_item(item_no);
         if (idx < 0) break;
         const int n_tiles = p.items[idx].n_tiles;
-        mbar_wait_bounded(&sm.q_full, item_no & 1u, abort_flag, p.status);
+        const int qb = item_no & 1u;
+        mbar_wait_bounded(&sm.q_full[qb], (item_no >> 1) & 1u, abort_flag, p.status);
+        const uint32_t q_lo = dq_lo + (uint32_t)((qb * kTcQBytes) >> 4);
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
           const int s = it % kTcKStages;
           const int b = it & 1u;
@@ -259,11 +297,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           tc_fence_after();
           const uint32_t k_lo = dk_lo + (uint32_t)((s * kPfTileBytes) >> 4);
           const uint32_t d_tmem = tmem + b * 128;
-          umma_bf16_ss_lo<false>(d_tmem, dq_lo, dq_hi, k_lo, dk_hi, idesc_qk);
+          umma_bf16_ss_lo<false>(d_tmem, q_lo, dq_hi, k_lo, dk_hi, idesc_qk);
 #pragma unroll
           for (int ks = 1; ks < kPfHeadDim / 16; ++ks) {
             const int half = ks >> 2;
-            umma_bf16_ss_lo<true>(d_tmem, dq_lo + (uint32_t)((half * (kPfRows * 128) + (ks & 3) * 32) >> 4),
+            umma_bf16_ss_lo<true>(d_tmem, q_lo + (uint32_t)((half * (kPfRows * 128) + (ks & 3) * 32) >> 4),
                                   dq_hi, k_lo + (uint32_t)((half * kPfHalfTileBytes + (ks & 3) * 32) >> 4),
                                   dk_hi, idesc_qk);
           }
@@ -271,6 +309,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           umma_commit(&sm.k_empty[s]);
           PF_TRACE(4, it);
         }
+        umma_commit(&sm.q_empty[qb]);          // the Q buffer may be refilled once these MMAs have run
       }
     }
     __syncwarp();
@@ -334,19 +373,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       const bool valid = rg < rows_total;
       const int64_t tok = item.q_start + (valid ? rg / G : 0);
       const int head = item.kv_head * G + (valid ? rg % G : 0);
-      // ---- Q row -> shared memory (K-major, 128-byte swizzle), zero for unused rows;
-      // each group copies one 64-dim half of the row
-      {
-        const uint4* src = reinterpret_cast<const uint4*>(p.q + tok * p.q_stride + (int64_t)head * kPfHeadDim) + g * 8;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (valid) v = __ldg(src + c);
-          *reinterpret_cast<uint4*>(sm.q + g * (kPfRows * 128) + swz128(r, c)) = v;
-        }
-        fence_proxy_async_smem();
-        mbar_arrive(&sm.q_full);
-      }
       const int lim = valid ? min(item.causal_base + rg / G, item.kv_len - 1) : -1;
       float m_used = -INFINITY;      // maximum the group's accumulators are scaled to (may lag behind)
       float l = 0.f;
