@@ -25,7 +25,7 @@ class DecodePlanInfo(ctypes.Structure):
 
 class PrefillPlanInfo(ctypes.Structure):
     """Mirror of ``b200_prefill_plan_info``."""
-    _fields_ = [(name, c_int32) for name in ("num_items", "total_tiles", "plan_ints", "reserved")]
+    _fields_ = [(name, c_int32) for name in ("num_items", "total_tiles", "plan_ints", "num_tokens")]
 
 
 # name -> (restype, argtypes); one entry per function the header declares

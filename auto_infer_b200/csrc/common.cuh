@@ -21,6 +21,12 @@ int check_cuda(cudaError_t err, const char* what);
 int get_cache_tensor_map(const void* cache, int num_blocks, int block_size, int heads, int dim,
                          int box_tokens, CUtensorMap* out);
 
+// Encodes (and memoises) a 3-D tiled tensor map over the query activations
+// (num_tokens, heads, 128) bf16 whose box is one 128-row query tile of a kv
+// group: 64 dims x group heads x (128 / group) tokens, 128-byte swizzle.
+int get_query_tensor_map(const void* q, int num_tokens, int heads, int64_t token_stride, int group,
+                         CUtensorMap* out);
+
 // ---- device ---------------------------------------------------------------
 #ifdef __CUDACC__
 
@@ -125,6 +131,16 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)),
         "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)),
+        "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 

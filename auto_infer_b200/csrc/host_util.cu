@@ -106,6 +106,63 @@ int get_cache_tensor_map(const void* cache, int num_blocks, int block_size, int 
   return B200_OK;
 }
 
+struct QMapKey {
+  const void* ptr;
+  int num_tokens, heads, group, device;
+  int64_t token_stride;
+  bool operator==(const QMapKey& o) const {
+    return ptr == o.ptr && num_tokens == o.num_tokens && heads == o.heads && group == o.group &&
+           device == o.device && token_stride == o.token_stride;
+  }
+};
+struct QMapEntry {
+  QMapKey key;
+  CUtensorMap map;
+};
+
+int get_query_tensor_map(const void* q, int num_tokens, int heads, int64_t token_stride, int group,
+                         CUtensorMap* out) {
+  static std::mutex mu;
+  static std::vector<QMapEntry> entries;
+  int device = 0;
+  cudaGetDevice(&device);
+  QMapKey key{q, num_tokens, heads, group, device, token_stride};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const QMapEntry& e : entries)
+      if (e.key == key) {
+        *out = e.map;
+        return B200_OK;
+      }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) {
+    set_last_error("cuTensorMapEncodeTiled is not available from this driver");
+    return B200_ECUDA;
+  }
+  // innermost first: dim, head, token
+  cuuint64_t dims[3] = {128, (cuuint64_t)heads, (cuuint64_t)num_tokens};
+  cuuint64_t strides[2] = {128 * 2, (cuuint64_t)token_stride * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)group, (cuuint32_t)(128 / group)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap map;
+  CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled failed with CUresult %d (query: tokens=%d heads=%d group=%d)",
+                   (int)r, num_tokens, heads, group);
+    return B200_ECUDA;
+  }
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (entries.size() >= 64) entries.erase(entries.begin());
+    entries.push_back(QMapEntry{key, map});
+  }
+  *out = map;
+  return B200_OK;
+}
+
 }  // namespace b200
 
 extern "C" {

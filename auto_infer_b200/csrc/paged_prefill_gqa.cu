@@ -45,6 +45,7 @@ struct PrefillParams {
   int num_q_heads, group;
   int block_size, block_shift, num_blocks, box_tokens, boxes_per_tile;
   int out_is_f32;
+  int q_by_tma;                     // the Q tile is one TMA box (else copied row by row)
   float scale, scale_log2;
 #ifdef B200_TRACE
   long long* trace;                 // clock64 samples of CTA 0 (debug builds)
@@ -69,17 +70,23 @@ struct PrefillParams {
 //   warp  8     TMA producer of 64-token K and V tiles (separate rings)
 //   warp  9     tensor-memory owner, issues S = Q K^T
 //   warp  10    issues O += P V
-// Per 128-token KV tile j: S_j = Q K_j^T (M 128, N 128, 8 x K16) lands in one of
-// two S buffers; group g owns columns [64 g, 64 g + 64) of it (tokens 64 g ... of
-// the tile): its threads read their row with tcgen05.ld (a thread holds a whole
-// row: no shuffles), write P as bf16 in the 128-byte-swizzled K-major layout, and
-// O_g (+)= P_g V_j[64 g ...] (M 128, N 128, 4 x K16, V read MN-major from the TMA
-// tile) accumulates in the group's own O buffer under the group's own running
-// maximum.  The groups are thus a split of the keys; their (m, l, O) are merged
-// at the end of an item, each group writing half of the output columns.  The
-// MMAs are queued by two dedicated threads, so S of the next tile is in flight
-// while the exponentials of this one run.  O is rescaled in tensor memory only
-// when a row maximum grows by more than 2^8 (the stale maximum is kept otherwise).
+// 128-token KV tile j of the running sequence belongs to group j & 1 and uses S
+// buffer j % 3: S_j = Q K_j^T (M 128, N 128, 8 x K16) lands there, the group's
+// threads read their row with tcgen05.ld (a thread holds a whole row: no
+// shuffles) and write P as packed bf16 back into the second half of the same
+// columns; the MMA reads it from tensor memory as its A operand: O (+)= P V_j
+// (M 128, N 128, 8 x K16, V read MN-major from the TMA tile).  Both groups
+// accumulate into ONE O under ONE running maximum per row, handed from the owner
+// of tile j to the owner of tile j + 1 through shared memory right after the row
+// maximum of tile j is known, so the groups run half a tile out of phase: while
+// one is in its exponentials (the MUFU floor of the kernel) the other loads,
+// stores or reduces.  With three S buffers the S of a group's next tile is ready
+// before the group has finished the current one (P aliases S, so a buffer is
+// busy until its P V has run).  Each group keeps its own row sum; the sums are
+// merged at the end of an item, each group writing half of the output columns.
+// The MMAs are queued by two dedicated threads.  O is rescaled in tensor memory
+// only when a row maximum grows by more than 2^8 (the stale maximum is kept
+// otherwise).
 // N = 128 per MMA on purpose: a tcgen05.mma costs ~50 cycles to issue whatever its
 // size, so N = 64 instructions (32 cycles of math) would leave the pipe waiting.
 // ============================================================================
@@ -87,28 +94,32 @@ constexpr int kTcKStages = 2;             // 32 KB per stage
 constexpr int kTcVStages = 3;
 constexpr int kTcSoftmaxThreads = 256;
 constexpr int kTcThreads = kTcSoftmaxThreads + 96;
-constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O_A [256,384) O_B [384,512)
+constexpr int kTcSBufs = 3;
+constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) S2 [256,384) O [384,512)
+constexpr int kTcOCol = 384;
 constexpr int kTcQBytes = 2 * kPfRows * 128;
 
 struct __align__(1024) TcSmem {
   uint8_t q[2][kTcQBytes];                 // per item parity: [dim half][128 rows][128 B], swizzled
   uint8_t k[kTcKStages][kPfTileBytes];     // [dims 0-63 | dims 64-127], 128 tokens x 128 B each
   uint8_t v[kTcVStages][kPfTileBytes];
-  float row_m[2][kPfRows];                 // end-of-item exchange of the groups' row state
-  float row_l[2][kPfRows];
+  float row_l[2][kPfRows];                 // end-of-item exchange of the groups' row sums
+  float row_ms[2][kPfRows];                // running row maximum after tile j, slot j & 1
   uint64_t k_full[kTcKStages];
   uint64_t k_empty[kTcKStages];
   uint64_t v_full[kTcVStages];
   uint64_t v_empty[kTcVStages];
-  uint64_t s_full[2];
-  uint64_t s_empty[2];
-  uint64_t p_full[2];
-  uint64_t pv_done[2];
+  uint64_t s_full[kTcSBufs];
+  uint64_t s_empty[kTcSBufs];
+  uint64_t p_full[2];                      // per group
+  uint64_t pv_done[2];                     // per tile parity
+  uint64_t m_ready[2];                     // per tile parity: row_ms[parity] is written
   uint64_t o_done;
   uint64_t q_full[2];                      // producer warp -> S issuer: the item's Q tile is staged
   uint64_t q_empty[2];                     // S issuer -> producer warp: all S MMAs of the item have run
   uint64_t item_full[2];                   // work-queue hand-off: producer warp -> the other roles
   uint64_t item_empty[2];
+  alignas(16) PrefillItem next_rec[2];     // the mailbox carries the whole item record (read as int4)
   int next_item[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -117,7 +128,8 @@ static_assert(sizeof(TcSmem) <= 227 * 1024, "shared memory budget of one CTA");
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
-                        const __grid_constant__ CUtensorMap v_map, const PrefillParams p) {
+                        const __grid_constant__ CUtensorMap v_map,
+                        const __grid_constant__ CUtensorMap q_map, const PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   TcSmem& sm = *reinterpret_cast<TcSmem*>(smem_raw);
   const int warp = threadIdx.x >> 5;
@@ -137,18 +149,21 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kTcSBufs; ++b) {
       mbar_init(&sm.s_full[b], 1);
       mbar_init(&sm.s_empty[b], 1);                // committed by the P V issuer: P aliases S
+    }
+    for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.p_full[b], 128);
       mbar_init(&sm.pv_done[b], 1);
+      mbar_init(&sm.m_ready[b], 128);
       mbar_init(&sm.item_full[b], 1);
       mbar_init(&sm.item_empty[b], kTcSoftmaxThreads + 2);   // softmax threads + the two MMA threads
     }
     mbar_init(&sm.o_done, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.q_full[b], 32);
-      mbar_init(&sm.q_empty[b], 1);
+      mbar_init(&sm.q_empty[b], 1 + kTcSoftmaxThreads);   // S issuer's commit + the epilogue's staging use
     }
     mbar_fence_init();
   }
@@ -165,9 +180,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   // Items are handed out dynamically, longest first: the producer warp draws the
   // next index from a global counter and passes it to the other roles through a
   // two-slot mailbox.  -1 ends the CTA.
-  auto take_item = [&](uint32_t k) -> int {
+  auto take_item = [&](uint32_t k, PrefillItem& rec) -> int {
     mbar_wait_bounded(&sm.item_full[k & 1u], (k >> 1) & 1u, abort_flag, p.status);
     const int idx = *reinterpret_cast<volatile int*>(&sm.next_item[k & 1u]);
+    const int4* src = reinterpret_cast<const int4*>(&sm.next_rec[k & 1u]);
+    const int4 lo = src[0], hi = src[1];
+    rec = PrefillItem{lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     mbar_arrive(&sm.item_empty[k & 1u]);
     return (*abort_flag || idx < 0 || idx >= p.num_items) ? -1 : idx;
   };
@@ -177,6 +195,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     if (lane == 0) {
       tma_prefetch_desc(&k_map);
       tma_prefetch_desc(&v_map);
+      if (p.q_by_tma) tma_prefetch_desc(&q_map);
     }
     uint32_t it = 0;
     const int nbox = p.boxes_per_tile;
@@ -186,43 +205,64 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         idx = atomicAdd(p.work_counter, 1);
         if (idx >= p.num_items || *abort_flag) idx = -1;
         mbar_wait_bounded(&sm.item_empty[k & 1u], ((k >> 1) & 1u) ^ 1u, abort_flag, p.status);
+        if (idx >= 0) {
+          const int4* src = reinterpret_cast<const int4*>(p.items + idx);
+          int4* dst = reinterpret_cast<int4*>(&sm.next_rec[k & 1u]);
+          dst[0] = __ldg(src);
+          dst[1] = __ldg(src + 1);
+        }
         sm.next_item[k & 1u] = idx;
-        mbar_arrive(&sm.item_full[k & 1u]);     // release semantics: the index is visible to waiters
+        mbar_arrive(&sm.item_full[k & 1u]);     // release semantics: index and record are visible to waiters
       }
       idx = __shfl_sync(0xffffffffu, idx, 0);
       if (idx < 0) break;
-      const PrefillItem item = p.items[idx];
-      // ---- stage the item's Q tile (K-major, 128-byte swizzle, zero for unused rows) in the
-      // buffer of its parity, one item ahead of the MMAs: lane l copies rows l, l+32, ...
+      const PrefillItem item = sm.next_rec[k & 1u];   // not overwritten before this warp draws item k + 2
+      // ---- stage the item's Q tile (K-major, 128-byte swizzle) in the buffer of its parity,
+      // one item ahead of the MMAs.  Rows are (token, head of the kv group) pairs, head
+      // fastest: exactly one TMA box of group heads x 128 / group tokens per half of the
+      // dims when 128 is a multiple of the group (rows past the sequence then hold other
+      // tokens' queries or zeros: their scores are masked and nothing of them is stored).
       {
         const int qb = k & 1u;
         if (lane == 0) mbar_wait_bounded(&sm.q_empty[qb], ((k >> 1) & 1u) ^ 1u, abort_flag, p.status);
         __syncwarp();
-        const int rows_total = item.q_len * p.group;
+        if (p.q_by_tma) {
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&sm.q_full[qb], kTcQBytes);
+            const int tok0 = item.q_start + item.row0 / p.group;
+            tma_load_3d(sm.q[qb], &q_map, &sm.q_full[qb], 0, item.kv_head * p.group, tok0);
+            tma_load_3d(sm.q[qb] + kPfRows * 128, &q_map, &sm.q_full[qb], 64, item.kv_head * p.group, tok0);
+          } else {
+            mbar_arrive(&sm.q_full[qb]);
+          }
+        } else {
+          // lane l copies rows l, l+32, ... (zero for unused rows)
+          const int rows_total = item.q_len * p.group;
 #pragma unroll 1
-        for (int rr = 0; rr < kPfRows; rr += 64) {
-          uint4 v[2][16];
+          for (int rr = 0; rr < kPfRows; rr += 64) {
+            uint4 v[2][16];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int r = rr + h * 32 + lane;
-            const int rg = item.row0 + r;
-            const bool valid = rg < rows_total;
-            const uint4* src = reinterpret_cast<const uint4*>(
-                p.q + (int64_t)(item.q_start + (valid ? rg / p.group : 0)) * p.q_stride +
-                (int64_t)(item.kv_head * p.group + (valid ? rg % p.group : 0)) * kPfHeadDim);
+            for (int h = 0; h < 2; ++h) {
+              const int r = rr + h * 32 + lane;
+              const int rg = item.row0 + r;
+              const bool valid = rg < rows_total;
+              const uint4* src = reinterpret_cast<const uint4*>(
+                  p.q + (int64_t)(item.q_start + (valid ? rg / p.group : 0)) * p.q_stride +
+                  (int64_t)(item.kv_head * p.group + (valid ? rg % p.group : 0)) * kPfHeadDim);
 #pragma unroll
-            for (int c = 0; c < 16; ++c) v[h][c] = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+              for (int c = 0; c < 16; ++c) v[h][c] = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int r = rr + h * 32 + lane;
+#pragma unroll
+              for (int c = 0; c < 16; ++c)
+                *reinterpret_cast<uint4*>(sm.q[qb] + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v[h][c];
+            }
           }
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int r = rr + h * 32 + lane;
-#pragma unroll
-            for (int c = 0; c < 16; ++c)
-              *reinterpret_cast<uint4*>(sm.q[qb] + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v[h][c];
-          }
+          fence_proxy_async_smem();
+          mbar_arrive(&sm.q_full[qb]);
         }
-        fence_proxy_async_smem();
-        mbar_arrive(&sm.q_full[qb]);
       }
       const int last_block = (item.kv_len - 1) >> p.block_shift;
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
@@ -283,17 +323,17 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       const uint32_t dk_lo = (uint32_t)dk, dk_hi = (uint32_t)(dk >> 32);
       uint32_t it = 0;
       for (uint32_t item_no = 0;; ++item_no) {
-        const int idx = take_item(item_no);
-        if (idx < 0) break;
-        const int n_tiles = p.items[idx].n_tiles;
+        PrefillItem rec;
+        if (take_item(item_no, rec) < 0) break;
+        const int n_tiles = rec.n_tiles;
         const int qb = item_no & 1u;
         mbar_wait_bounded(&sm.q_full[qb], (item_no >> 1) & 1u, abort_flag, p.status);
         const uint32_t q_lo = dq_lo + (uint32_t)((qb * kTcQBytes) >> 4);
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
           const int s = it % kTcKStages;
-          const int b = it & 1u;
+          const int b = it % kTcSBufs;
           mbar_wait_bounded(&sm.k_full[s], (it / kTcKStages) & 1u, abort_flag, p.status);
-          mbar_wait_bounded(&sm.s_empty[b], ((it >> 1) & 1u) ^ 1u, abort_flag, p.status);
+          mbar_wait_bounded(&sm.s_empty[b], ((it / kTcSBufs) & 1u) ^ 1u, abort_flag, p.status);
           tc_fence_after();
           const uint32_t k_lo = dk_lo + (uint32_t)((s * kPfTileBytes) >> 4);
           const uint32_t d_tmem = tmem + b * 128;
@@ -321,34 +361,31 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       const uint32_t dv_lo = (uint32_t)dv, dv_hi = (uint32_t)(dv >> 32);
       uint32_t it = 0;
       for (uint32_t item_no = 0;; ++item_no) {
-        const int idx = take_item(item_no);
-        if (idx < 0) break;
-        const int n_tiles = p.items[idx].n_tiles;
+        PrefillItem rec;
+        if (take_item(item_no, rec) < 0) break;
+        const int n_tiles = rec.n_tiles;
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
           const int s = it % kTcVStages;
+          const int g = it & 1u;                            // the group that owns this tile
+          const int b = it % kTcSBufs;
           mbar_wait_bounded(&sm.v_full[s], (it / kTcVStages) & 1u, abort_flag, p.status);
+          mbar_wait_bounded(&sm.p_full[g], (it >> 1) & 1u, abort_flag, p.status);
+          tc_fence_after();
+          PF_TRACE(5, it);
           const uint32_t v_lo = dv_lo + (uint32_t)((s * kPfTileBytes) >> 4);
+          // P of the tile: bf16 pairs in the last 64 columns of its S buffer
+          const uint32_t p_tmem = tmem + b * 128 + 64;
+          const uint32_t d_tmem = tmem + kTcOCol;
+          if (tile == 0)                                    // the first tile of the item overwrites
+            umma_bf16_ts_lo<false>(d_tmem, p_tmem, v_lo, dv_hi, idesc_pv);
+          else
+            umma_bf16_ts_lo<true>(d_tmem, p_tmem, v_lo, dv_hi, idesc_pv);
 #pragma unroll
-          for (int g = 0; g < 2; ++g) {
-            mbar_wait_bounded(&sm.p_full[g], it & 1u, abort_flag, p.status);
-            tc_fence_after();
-            PF_TRACE(5 + g * 4, it);
-            // P of the group: bf16 pairs in the first 32 columns of the group's half of the S buffer
-            const uint32_t p_tmem = tmem + (it & 1u) * 128 + g * 64;
-            const uint32_t vg_lo = v_lo + (uint32_t)((g * 64 * 128) >> 4);   // the group's 64 tokens of the tile
-            const uint32_t d_tmem = tmem + 256 + g * 128;
-            if (tile == 0)                                  // first tile of the item overwrites
-              umma_bf16_ts_lo<false>(d_tmem, p_tmem, vg_lo, dv_hi, idesc_pv);
-            else
-              umma_bf16_ts_lo<true>(d_tmem, p_tmem, vg_lo, dv_hi, idesc_pv);
-#pragma unroll
-            for (int ks = 1; ks < 4; ++ks)
-              umma_bf16_ts_lo<true>(d_tmem, p_tmem + ks * 8, vg_lo + (uint32_t)((ks * 2048) >> 4), dv_hi,
-                                    idesc_pv);
-            umma_commit(&sm.pv_done[g]);
-          }
+          for (int ks = 1; ks < kPfTile / 16; ++ks)
+            umma_bf16_ts_lo<true>(d_tmem, p_tmem + ks * 8, v_lo + (uint32_t)((ks * 2048) >> 4), dv_hi, idesc_pv);
+          umma_commit(&sm.pv_done[g]);
           umma_commit(&sm.v_empty[s]);
-          umma_commit(&sm.s_empty[it & 1u]);                // S buffer (and the P inside it) may be overwritten
+          umma_commit(&sm.s_empty[b]);                      // S buffer (and the P inside it) may be overwritten
           PF_TRACE(6, it);
         }
         umma_commit(&sm.o_done);
@@ -357,81 +394,106 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     __syncwarp();
   } else {
     // --------------------------- softmax + epilogue ---------------------------
-    const int g = warp >> 2;                         // group: tokens [64 g, 64 g + 64) of every KV tile
+    const int g = warp >> 2;                         // group: KV tiles whose running index & 1 == g
     const int r = threadIdx.x & 127;                 // query row of the tile == TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t s_col = lane_base + g * 64;       // + 128 * (tile & 1)
-    const uint32_t o_col = lane_base + 256 + g * 128;
+    const uint32_t o_col = lane_base + kTcOCol;
     const int G = p.group;
     uint32_t it = 0;
     for (uint32_t item_no = 0;; ++item_no) {
-      const int idx = take_item(item_no);
-      if (idx < 0) break;
-      const PrefillItem item = p.items[idx];
+      PrefillItem item;
+      if (take_item(item_no, item) < 0) break;
       const int rows_total = item.q_len * G;
       const int rg = item.row0 + r;
       const bool valid = rg < rows_total;
       const int64_t tok = item.q_start + (valid ? rg / G : 0);
       const int head = item.kv_head * G + (valid ? rg % G : 0);
       const int lim = valid ? min(item.causal_base + rg / G, item.kv_len - 1) : -1;
-      float m_used = -INFINITY;      // maximum the group's accumulators are scaled to (may lag behind)
+      float m_ref = -INFINITY;       // maximum this group's row sum is scaled to
       float l = 0.f;
-      bool have_o = false;           // this group has issued at least one P V for the item
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
-        const int sb = it & 1u;                      // S buffer of this tile
+        if ((int)(it & 1u) != g) continue;             // the other group's tile
+        const uint32_t sb = it % kTcSBufs;
+        const uint32_t s_col = lane_base + sb * 128;   // P aliases the second half of the buffer
         if (r == 0) PF_TRACE(0 + g * 10, it);
-        mbar_wait_bounded(&sm.s_full[sb], (it >> 1) & 1u, abort_flag, p.status);
+        mbar_wait_bounded(&sm.s_full[sb], (it / kTcSBufs) & 1u, abort_flag, p.status);
         tc_fence_after();
         if (r == 0) PF_TRACE(1 + g * 10, it);
-        uint32_t sr[2][32];
-        tmem_ld32(s_col + sb * 128, sr[0]);
-        tmem_ld32(s_col + sb * 128 + 32, sr[1]);
-        tmem_wait_ld();
-        const int tbase = tile * kPfTile + g * 64;   // first token of this group's columns
-        if (tbase + 63 > lim) {
+        const int tbase = tile * kPfTile;
+        const bool need_mask = tbase + kPfTile - 1 > lim;
+        auto load_half = [&](int half, uint32_t (&sr)[2][32]) {
+          tmem_ld32(s_col + half * 64, sr[0]);
+          tmem_ld32(s_col + half * 64 + 32, sr[1]);
+          tmem_wait_ld();
+          if (need_mask) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int c = 0; c < 32; ++c)
-              if (tbase + h * 32 + c > lim) sr[h][c] = __float_as_uint(-INFINITY);
-        }
-        float mx;
-        {
+              for (int c = 0; c < 32; ++c)
+                if (tbase + half * 64 + h * 32 + c > lim) sr[h][c] = __float_as_uint(-INFINITY);
+          }
+        };
+        auto max_half = [&](const uint32_t (&sr)[2][32]) -> float {
           float mq[8];                      // eight independent chains instead of one of 64
 #pragma unroll
           for (int u = 0; u < 8; ++u) mq[u] = __uint_as_float(sr[0][u]);
 #pragma unroll
           for (int c = 8; c < 64; ++c) mq[c & 7] = fmaxf(mq[c & 7], __uint_as_float(sr[c >> 5][c & 31]));
-          mx = fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])),
-                     fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
+          return fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])),
+                       fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
+        };
+        // pass 1: row maximum over the tile's 128 columns (second half stays in registers)
+        uint32_t sr[2][32];
+        load_half(0, sr);
+        float mx = max_half(sr);
+        load_half(1, sr);
+        mx = fmaxf(mx, max_half(sr));
+        // the maximum O is scaled to after the previous tile (owned by the other group)
+        float m_in = -INFINITY;
+        if (tile > 0) {
+          mbar_wait_bounded(&sm.m_ready[(it - 1) & 1u], ((it - 1) >> 1) & 1u, abort_flag, p.status);
+          m_in = sm.row_ms[(it - 1) & 1u][r];
         }
-        // lazy rescale: only when some row of the warp outgrew its stale maximum by 2^8
-        const bool grow = (mx - m_used) * p.scale_log2 > 8.f || (m_used == -INFINITY && mx > -INFINITY);
+        // lazy rescale: only when some row of the warp outgrew the stale maximum by 2^8
+        const bool grow = (mx - m_in) * p.scale_log2 > 8.f || (m_in == -INFINITY && mx > -INFINITY);
         const bool rescale = __any_sync(0xffffffffu, grow);
-        float corr = 1.f;
-        if (rescale) {
-          const float m_new = fmaxf(m_used, mx);
-          corr = (m_used == -INFINITY) ? 0.f : fast_exp2((m_used - m_new) * p.scale_log2);
-          m_used = m_new;
-          l *= corr;
+        const float m_used = rescale ? fmaxf(m_in, mx) : m_in;
+        sm.row_ms[it & 1u][r] = m_used;
+        mbar_arrive(&sm.m_ready[it & 1u]);             // release: the next tile's owner may go on
+        const float corr = (!rescale) ? 1.f : (m_in == -INFINITY ? 0.f : fast_exp2((m_in - m_used) * p.scale_log2));
+        if (m_used != m_ref) {                         // bring this group's row sum to the new reference
+          l *= (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_used) * p.scale_log2);
+          m_ref = m_used;
         }
         const float ms = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
+        auto exp_half = [&](const uint32_t (&sr)[2][32], uint32_t (&pk)[32]) {
+          float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[h][c]), p.scale_log2, -ms));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[h][c + 1]), p.scale_log2, -ms));
+              ls[(c >> 1) & 3] += p0 + p1;
+              pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
+            }
+          l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        };
+        // pass 2: probabilities of the second half (already in registers), then the first
+        // half again.  P (128 tokens, bf16 pairs) goes to the second half of the S buffer,
+        // which is free as soon as its values are in registers.
         uint32_t pk[32];
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float p0 = fast_exp2(fmaf(__uint_as_float(sr[h][c]), p.scale_log2, -ms));
-            const float p1 = fast_exp2(fmaf(__uint_as_float(sr[h][c + 1]), p.scale_log2, -ms));
-            ls[(c >> 1) & 3] += p0 + p1;
-            pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
-          }
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        exp_half(sr, pk);
+        tmem_st32(s_col + 96, pk);
+        load_half(0, sr);
+        exp_half(sr, pk);
+        tmem_st32(s_col + 64, pk);
         if (r == 0) PF_TRACE(2 + g * 10, it);
-        // O may be touched once the group's previous P V is done (rare path)
-        if (rescale && have_o) {
-          mbar_wait_bounded(&sm.pv_done[g], (it - 1) & 1u, abort_flag, p.status);
+        // O may be touched once the previous tile's P V is done (rare path).  The barrier of
+        // that tile's parity has completed (it - 1) / 2 or (it - 1) / 2 + 1 phases here: the S
+        // just read could only be computed after the P V of tile it - 3 had run.
+        if (rescale && tile > 0) {
+          mbar_wait_bounded(&sm.pv_done[(it - 1) & 1u], ((it - 1) >> 1) & 1u, abort_flag, p.status);
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
@@ -442,73 +504,88 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             for (int i = 0; i < 32; ++i) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
             tmem_st32(o_col + c * 32, orow);
           }
-          tmem_wait_st();
         }
-        // P replaces the first half of the columns this thread has just read
-        tmem_st32(s_col + sb * 128, pk);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_full[g]);
         if (r == 0) PF_TRACE(3 + g * 10, it);
-        have_o = true;
       }
       if (r == 0 && g == 0) PF_TRACE(7, it > 0 ? it - 1 : 0);
-      // ---- merge the two groups and write the item: group g writes columns [64 g, 64 g + 64)
-      sm.row_m[g][r] = have_o ? m_used : -INFINITY;
-      sm.row_l[g][r] = have_o ? l : 0.f;
+      // ---- merge the groups' row sums and write the item: group g writes columns [64 g, 64 g + 64)
+      // the maxima only grow along the tiles: the last tile's is what O is scaled to
+      float mm = -INFINITY;
+      if (item.n_tiles > 0) {
+        mbar_wait_bounded(&sm.m_ready[(it - 1) & 1u], ((it - 1) >> 1) & 1u, abort_flag, p.status);
+        mm = sm.row_ms[(it - 1) & 1u][r];
+      }
+      sm.row_l[g][r] = (m_ref == -INFINITY) ? 0.f : l * fast_exp2((m_ref - mm) * p.scale_log2);
       mbar_wait_bounded(&sm.o_done, item_no & 1u, abort_flag, p.status);
       tc_fence_after();
+      if (r == 0 && g == 0) PF_TRACE(9, it > 0 ? it - 1 : 0);
       named_bar_sync(1, kTcSoftmaxThreads);
+      if (r == 0 && g == 0) PF_TRACE(14, it > 0 ? it - 1 : 0);
       {
-        const float ma = sm.row_m[0][r], mb = sm.row_m[1][r];
-        const float mm = fmaxf(ma, mb);
-        const float fa = (ma == -INFINITY) ? 0.f : fast_exp2((ma - mm) * p.scale_log2);
-        const float fb = (mb == -INFINITY) ? 0.f : fast_exp2((mb - mm) * p.scale_log2);
-        const float lsum = sm.row_l[0][r] * fa + sm.row_l[1][r] * fb;
+        const float lsum = sm.row_l[0][r] + sm.row_l[1][r];
         const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        const float wa = fa * inv, wb = fb * inv;
-        const bool use_a = ma != -INFINITY, use_b = mb != -INFINITY;   // warp-uniform? no: per row
-        const bool any_a = __any_sync(0xffffffffu, use_a), any_b = __any_sync(0xffffffffu, use_b);
+        if (p.out_is_f32) {
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          const int col = g * 64 + c * 32;
-          uint32_t oa[32], ob[32];
-          if (any_a) tmem_ld32(lane_base + 256 + col, oa);
-          if (any_b) tmem_ld32(lane_base + 384 + col, ob);
-          tmem_wait_ld();
-          float res[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float xa = use_a ? __uint_as_float(oa[i]) * wa : 0.f;   // never multiply unwritten TMEM
-            const float xb = use_b ? __uint_as_float(ob[i]) * wb : 0.f;
-            res[i] = xa + xb;
-          }
-          if (valid) {
-            const int64_t off = (tok * p.num_q_heads + head) * kPfHeadDim + col;
-            if (p.out_is_f32) {
-              float* dst = reinterpret_cast<float*>(p.out) + off;
+          for (int c = 0; c < 2; ++c) {
+            const int col = g * 64 + c * 32;
+            uint32_t o[32];
+            tmem_ld32(o_col + col, o);
+            tmem_wait_ld();
+            if (valid) {
+              float* dst = reinterpret_cast<float*>(p.out) + (tok * p.num_q_heads + head) * kPfHeadDim + col;
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<float4*>(dst + i) = make_float4(res[i], res[i + 1], res[i + 2], res[i + 3]);
-            } else {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 v;
-                v.x = pack_bf16(res[i], res[i + 1]);
-                v.y = pack_bf16(res[i + 2], res[i + 3]);
-                v.z = pack_bf16(res[i + 4], res[i + 5]);
-                v.w = pack_bf16(res[i + 6], res[i + 7]);
-                *reinterpret_cast<uint4*>(dst + i) = v;
-              }
+                *reinterpret_cast<float4*>(dst + i) =
+                    make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                                __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
             }
           }
+        } else {
+          // bf16 rows go through the item's Q buffer (all its MMAs have run): 128 rows of
+          // 256 B, 16-byte chunks XOR-swizzled by the row, then out in whole 256-byte rows
+          uint8_t* stage = sm.q[item_no & 1u];
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_col + g * 64 + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[8 * j]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
+              const int ch = g * 8 + c * 4 + j;
+              *reinterpret_cast<uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4)) = v;
+            }
+          }
+          named_bar_sync(1, kTcSoftmaxThreads);
+          const int ch = lane & 15;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = warp * 16 + 2 * i + (lane >> 4);
+            const int rgo = item.row0 + row;
+            if (rgo < rows_total) {
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + ((ch ^ (row & 15)) << 4));
+              const int64_t t = item.q_start + rgo / G;
+              const int h = item.kv_head * G + rgo % G;
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) +
+                                        (t * p.num_q_heads + h) * kPfHeadDim + ch * 8) = v;
+            }
+          }
+          fence_proxy_async_smem();      // the buffer is refilled by TMA next
         }
+        mbar_arrive(&sm.q_empty[item_no & 1u]);
         if (valid && p.lse_out && g == 0)
           p.lse_out[tok * p.num_q_heads + head] = lsum > 0.f ? mm * p.scale + __logf(lsum) : -INFINITY;
       }
       // nobody may start the next item (new Q, new P V into O) while the other
       // group still reads this item's accumulators or row state
+      if (r == 0 && g == 0) PF_TRACE(15, it > 0 ? it - 1 : 0);
       tc_fence_before();
       named_bar_sync(1, kTcSoftmaxThreads);
       if (r == 0 && g == 0) PF_TRACE(8, it > 0 ? it - 1 : 0);
@@ -595,7 +672,7 @@ extern "C" int b200_prefill_plan(const int32_t* cu_q, const int32_t* kv_lens,
   info->num_items = (int32_t)items.size();
   info->total_tiles = total_tiles > INT32_MAX ? INT32_MAX : (int32_t)total_tiles;
   info->plan_ints = kPlanHeaderInts + kPfItemInts * (int32_t)items.size();
-  info->reserved = 0;
+  info->num_tokens = num_tokens;
   return B200_OK;
 }
 
@@ -630,9 +707,9 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
     set_last_error("paged_prefill_gqa: block_size %d must be a power of two >= 8", block_size);
     return B200_EUNSUPPORTED;
   }
-  if (reinterpret_cast<uintptr_t>(q) % 4 || (q_stride % 2) || q_stride < (int64_t)num_q_heads * head_dim ||
-      reinterpret_cast<uintptr_t>(out) % 16) {
-    set_last_error("paged_prefill_gqa: q must be 4-byte aligned with an even stride >= Hq*D, out 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(q) % 16 || (q_stride % 8) || q_stride < (int64_t)num_q_heads * head_dim ||
+      reinterpret_cast<uintptr_t>(out) % 16 || reinterpret_cast<uintptr_t>(plan_dev) % 16) {
+    set_last_error("paged_prefill_gqa: q, out and the plan must be 16-byte aligned, the q token stride a multiple of 8 elements and >= Hq*D");
     return B200_EALIGN;
   }
   const int box_tokens = block_size < 64 ? block_size : 64;
@@ -642,7 +719,17 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   rc = get_cache_tensor_map(value_cache, num_blocks, block_size, num_kv_heads, head_dim, box_tokens, &v_map);
   if (rc) return rc;
 
+  // One TMA box per Q tile needs a group that divides 128.
+  const int group = num_q_heads / num_kv_heads;
+  const bool q_by_tma = kPfRows % group == 0 && info->num_tokens > 0;
+  CUtensorMap q_map = k_map;      // placeholder when the tile is copied row by row
+  if (q_by_tma) {
+    rc = get_query_tensor_map(q, info->num_tokens, num_q_heads, q_stride, group, &q_map);
+    if (rc) return rc;
+  }
+
   PrefillParams p;
+  p.q_by_tma = q_by_tma ? 1 : 0;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.q_stride = q_stride;
   p.block_table = block_table;
@@ -682,7 +769,7 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   if (grid <= 0) grid = 148;
   if (grid > info->num_items) grid = info->num_items;
   return check_cuda(launch_pdl(paged_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), smem_tc,
-                               static_cast<cudaStream_t>(stream), k_map, v_map, p),
+                               static_cast<cudaStream_t>(stream), k_map, v_map, q_map, p),
                     "paged_prefill_gqa launch");
   return check_cuda(cudaGetLastError(), "paged_prefill_gqa launch");
 }

@@ -151,7 +151,7 @@ typedef struct b200_prefill_plan_info {
   int32_t num_items;       /* 128-row work items                               */
   int32_t total_tiles;     /* 128-token KV tiles summed over the items          */
   int32_t plan_ints;       /* int32 words of the plan actually used            */
-  int32_t reserved;
+  int32_t num_tokens;      /* rows of q the plan covers (the last cu_seqlens_q) */
 } b200_prefill_plan_info;
 
 size_t b200_prefill_plan_bytes(int num_seqs, int num_tokens, int num_q_heads, int num_kv_heads);
