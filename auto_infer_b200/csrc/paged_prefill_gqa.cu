@@ -71,36 +71,40 @@ struct PrefillParams {
 //   warp  9     tensor-memory owner, issues S = Q K^T
 //   warp  10    issues O += P V
 // 128-token KV tile j of the running sequence belongs to group j & 1 and uses S
-// buffer j % 3: S_j = Q K_j^T (M 128, N 128, 8 x K16) lands there, the group's
+// buffer j & 1: S_j = Q K_j^T (M 128, N 128, 8 x K16) lands there, the group's
 // threads read their row with tcgen05.ld (a thread holds a whole row: no
-// shuffles) and write P as packed bf16 back into the second half of the same
-// columns; the MMA reads it from tensor memory as its A operand: O (+)= P V_j
-// (M 128, N 128, 8 x K16, V read MN-major from the TMA tile).  Both groups
-// accumulate into ONE O under ONE running maximum per row, handed from the owner
-// of tile j to the owner of tile j + 1 through shared memory right after the row
-// maximum of tile j is known, so the groups run half a tile out of phase: while
-// one is in its exponentials (the MUFU floor of the kernel) the other loads,
-// stores or reduces.  With three S buffers the S of a group's next tile is ready
-// before the group has finished the current one (P aliases S, so a buffer is
-// busy until its P V has run).  Each group keeps its own row sum; the sums are
-// merged at the end of an item, each group writing half of the output columns.
+// shuffles), hand the buffer back as soon as its values are in registers, and
+// write P as packed bf16 into a tensor-memory buffer of its own; the MMA reads it
+// from there as its A operand: O (+)= P V_j (M 128, N 128, 8 x K16, V read
+// MN-major from the TMA tile).  Both groups accumulate into ONE O under ONE
+// running maximum per row, handed from the owner of tile j to the owner of tile
+// j + 1 through shared memory right after the row maximum of tile j is known, so
+// the groups run half a tile out of phase: while one is in its exponentials (the
+// MUFU floor of the kernel) the other loads, stores or reduces.  Each group keeps
+// its own row sum; the sums are merged at the end of an item.
+// Measured on the part: an M 128 x N 128 x K 16 MMA takes 67 cycles with both
+// operands in shared memory (8 KB read: all the bandwidth an SM has) and 100 cycles
+// with A in tensor memory whatever N <= 128 is, so S = Q K^T keeps Q in shared
+// memory and only P, which the threads produce in registers anyway, goes through
+// tensor memory (two buffers, one per group).
 // The MMAs are queued by two dedicated threads.  O is rescaled in tensor memory
 // only when a row maximum grows by more than 2^8 (the stale maximum is kept
 // otherwise).
 // N = 128 per MMA on purpose: a tcgen05.mma costs ~50 cycles to issue whatever its
 // size, so N = 64 instructions (32 cycles of math) would leave the pipe waiting.
 // ============================================================================
-constexpr int kTcKStages = 2;             // 32 KB per stage
+constexpr int kTcKStages = 3;             // 32 KB per stage
 constexpr int kTcVStages = 3;
+constexpr int kTcKLead = 1;               // K loads run this many tiles ahead of the V loads
 constexpr int kTcSoftmaxThreads = 256;
 constexpr int kTcThreads = kTcSoftmaxThreads + 96;
-constexpr int kTcSBufs = 3;
-constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) S2 [256,384) O [384,512)
-constexpr int kTcOCol = 384;
+constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O [256,384) P_A [384,448) P_B [448,512)
+constexpr int kTcOCol = 256;
+constexpr int kTcPCol = 384;
 constexpr int kTcQBytes = 2 * kPfRows * 128;
 
 struct __align__(1024) TcSmem {
-  uint8_t q[2][kTcQBytes];                 // per item parity: [dim half][128 rows][128 B], swizzled
+  uint8_t q[kTcQBytes];                    // [dim half][128 rows][128 B], swizzled
   uint8_t k[kTcKStages][kPfTileBytes];     // [dims 0-63 | dims 64-127], 128 tokens x 128 B each
   uint8_t v[kTcVStages][kPfTileBytes];
   float row_l[2][kPfRows];                 // end-of-item exchange of the groups' row sums
@@ -109,14 +113,14 @@ struct __align__(1024) TcSmem {
   uint64_t k_empty[kTcKStages];
   uint64_t v_full[kTcVStages];
   uint64_t v_empty[kTcVStages];
-  uint64_t s_full[kTcSBufs];
-  uint64_t s_empty[kTcSBufs];
+  uint64_t s_full[2];
+  uint64_t s_empty[2];                     // softmax threads: the tile's scores are in registers
   uint64_t p_full[2];                      // per group
   uint64_t pv_done[2];                     // per tile parity
   uint64_t m_ready[2];                     // per tile parity: row_ms[parity] is written
   uint64_t o_done;
-  uint64_t q_full[2];                      // producer warp -> S issuer: the item's Q tile is staged
-  uint64_t q_empty[2];                     // S issuer -> producer warp: all S MMAs of the item have run
+  uint64_t q_full;                         // producer warp: the item's Q tile is staged
+  uint64_t q_empty;                        // all S MMAs of the item have run
   uint64_t item_full[2];                   // work-queue hand-off: producer warp -> the other roles
   uint64_t item_empty[2];
   alignas(16) PrefillItem next_rec[2];     // the mailbox carries the whole item record (read as int4)
@@ -149,11 +153,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       mbar_init(&sm.v_full[s], 1);
       mbar_init(&sm.v_empty[s], 1);
     }
-    for (int b = 0; b < kTcSBufs; ++b) {
-      mbar_init(&sm.s_full[b], 1);
-      mbar_init(&sm.s_empty[b], 1);                // committed by the P V issuer: P aliases S
-    }
     for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.s_full[b], 1);
+      mbar_init(&sm.s_empty[b], 128);
       mbar_init(&sm.p_full[b], 128);
       mbar_init(&sm.pv_done[b], 1);
       mbar_init(&sm.m_ready[b], 128);
@@ -161,10 +163,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       mbar_init(&sm.item_empty[b], kTcSoftmaxThreads + 2);   // softmax threads + the two MMA threads
     }
     mbar_init(&sm.o_done, 1);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&sm.q_full[b], 32);
-      mbar_init(&sm.q_empty[b], 1 + kTcSoftmaxThreads);   // S issuer's commit + the epilogue's staging use
-    }
+    mbar_init(&sm.q_full, 32);
+    mbar_init(&sm.q_empty, 1);
     mbar_fence_init();
   }
   if (warp == 9) {
@@ -217,23 +217,22 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       idx = __shfl_sync(0xffffffffu, idx, 0);
       if (idx < 0) break;
       const PrefillItem item = sm.next_rec[k & 1u];   // not overwritten before this warp draws item k + 2
-      // ---- stage the item's Q tile (K-major, 128-byte swizzle) in the buffer of its parity,
-      // one item ahead of the MMAs.  Rows are (token, head of the kv group) pairs, head
+      // ---- stage the item's Q tile (K-major, 128-byte swizzle) as soon as the previous item's
+      // last S MMA has run, about a tile and an epilogue before it is needed.  Rows are (token, head of the kv group) pairs, head
       // fastest: exactly one TMA box of group heads x 128 / group tokens per half of the
       // dims when 128 is a multiple of the group (rows past the sequence then hold other
       // tokens' queries or zeros: their scores are masked and nothing of them is stored).
       {
-        const int qb = k & 1u;
-        if (lane == 0) mbar_wait_bounded(&sm.q_empty[qb], ((k >> 1) & 1u) ^ 1u, abort_flag, p.status);
+        if (lane == 0) mbar_wait_bounded(&sm.q_empty, (k & 1u) ^ 1u, abort_flag, p.status);
         __syncwarp();
         if (p.q_by_tma) {
           if (lane == 0) {
-            mbar_arrive_expect_tx(&sm.q_full[qb], kTcQBytes);
+            mbar_arrive_expect_tx(&sm.q_full, kTcQBytes);
             const int tok0 = item.q_start + item.row0 / p.group;
-            tma_load_3d(sm.q[qb], &q_map, &sm.q_full[qb], 0, item.kv_head * p.group, tok0);
-            tma_load_3d(sm.q[qb] + kPfRows * 128, &q_map, &sm.q_full[qb], 64, item.kv_head * p.group, tok0);
+            tma_load_3d(sm.q, &q_map, &sm.q_full, 0, item.kv_head * p.group, tok0);
+            tma_load_3d(sm.q + kPfRows * 128, &q_map, &sm.q_full, 64, item.kv_head * p.group, tok0);
           } else {
-            mbar_arrive(&sm.q_full[qb]);
+            mbar_arrive(&sm.q_full);
           }
         } else {
           // lane l copies rows l, l+32, ... (zero for unused rows)
@@ -257,15 +256,19 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
               const int r = rr + h * 32 + lane;
 #pragma unroll
               for (int c = 0; c < 16; ++c)
-                *reinterpret_cast<uint4*>(sm.q[qb] + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v[h][c];
+                *reinterpret_cast<uint4*>(sm.q + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v[h][c];
             }
           }
           fence_proxy_async_smem();
-          mbar_arrive(&sm.q_full[qb]);
+          mbar_arrive(&sm.q_full);
         }
       }
       const int last_block = (item.kv_len - 1) >> p.block_shift;
-      for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
+      // K and V travel through separate rings: a K stage is free again as soon as
+      // S = Q K^T has run, long before the V stage of the same tile (held until P V has
+      // run).  So the K loads run kTcKLead tiles ahead of the V loads: a full V ring does
+      // not keep the next K, which the S MMA needs first, from being requested.
+      auto issue = [&](bool is_k, int tile, uint32_t itx) {
         int bid = 0;
         const int token0 = tile * kPfTile + lane * p.box_tokens;     // first token of this lane's box
         if (lane < nbox) {
@@ -278,31 +281,39 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           bid = p.num_blocks;
         }
         const int tok = token0 & (p.block_size - 1);
-        // K and V travel through separate rings: a K stage is free again as soon as
-        // S = Q K^T has run, one step earlier than the V stage of the same tile
-        const int sk = it % kTcKStages, sv = it % kTcVStages;
-        if (lane == 0) {
-          mbar_wait_bounded(&sm.k_empty[sk], ((it / kTcKStages) & 1u) ^ 1u, abort_flag, p.status);
-          mbar_arrive_expect_tx(&sm.k_full[sk], kPfTileBytes);
+        if (is_k) {
+          const int sk = itx % kTcKStages;
+          if (lane == 0) {
+            mbar_wait_bounded(&sm.k_empty[sk], ((itx / kTcKStages) & 1u) ^ 1u, abort_flag, p.status);
+            mbar_arrive_expect_tx(&sm.k_full[sk], kPfTileBytes);
+          }
+          __syncwarp();
+          if (lane < nbox) {
+            uint8_t* dst = sm.k[sk] + lane * p.box_tokens * 128;
+            tma_load_4d(dst, &k_map, &sm.k_full[sk], 0, item.kv_head, tok, bid);
+            tma_load_4d(dst + kPfHalfTileBytes, &k_map, &sm.k_full[sk], 64, item.kv_head, tok, bid);
+          }
+        } else {
+          const int sv = itx % kTcVStages;
+          if (lane == 0) {
+            mbar_wait_bounded(&sm.v_empty[sv], ((itx / kTcVStages) & 1u) ^ 1u, abort_flag, p.status);
+            mbar_arrive_expect_tx(&sm.v_full[sv], kPfTileBytes);
+          }
+          __syncwarp();
+          if (lane < nbox) {
+            uint8_t* dst = sm.v[sv] + lane * p.box_tokens * 128;
+            tma_load_4d(dst, &v_map, &sm.v_full[sv], 0, item.kv_head, tok, bid);
+            tma_load_4d(dst + kPfHalfTileBytes, &v_map, &sm.v_full[sv], 64, item.kv_head, tok, bid);
+          }
         }
         __syncwarp();
-        if (lane < nbox) {
-          uint8_t* dst = sm.k[sk] + lane * p.box_tokens * 128;
-          tma_load_4d(dst, &k_map, &sm.k_full[sk], 0, item.kv_head, tok, bid);
-          tma_load_4d(dst + kPfHalfTileBytes, &k_map, &sm.k_full[sk], 64, item.kv_head, tok, bid);
-        }
-        if (lane == 0) {
-          mbar_wait_bounded(&sm.v_empty[sv], ((it / kTcVStages) & 1u) ^ 1u, abort_flag, p.status);
-          mbar_arrive_expect_tx(&sm.v_full[sv], kPfTileBytes);
-        }
-        __syncwarp();
-        if (lane < nbox) {
-          uint8_t* dst = sm.v[sv] + lane * p.box_tokens * 128;
-          tma_load_4d(dst, &v_map, &sm.v_full[sv], 0, item.kv_head, tok, bid);
-          tma_load_4d(dst + kPfHalfTileBytes, &v_map, &sm.v_full[sv], 64, item.kv_head, tok, bid);
-        }
-        __syncwarp();
+      };
+      int kt = 0;                                  // next K tile to request
+      for (int tile = 0; tile < item.n_tiles; ++tile) {
+        for (; kt < item.n_tiles && kt <= tile + kTcKLead; ++kt) issue(true, kt, it + kt);
+        issue(false, tile, it + tile);
       }
+      it += item.n_tiles;
     }
     if (lane == 0) {   // drain: nothing may still be landing when the CTA leaves
       for (uint32_t k = 0; k < (uint32_t)kTcVStages && k < it; ++k) {
@@ -317,7 +328,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(kPfRows, kPfTile, false);
       // descriptors differ only in their start-address field: build once, add offsets
-      const uint64_t dq = umma_desc_sw128(smem_u32(sm.q[0]), 16, 1024);
+      const uint64_t dq = umma_desc_sw128(smem_u32(sm.q), 16, 1024);
       const uint64_t dk = umma_desc_sw128(smem_u32(sm.k[0]), 16, 1024);
       const uint32_t dq_lo = (uint32_t)dq, dq_hi = (uint32_t)(dq >> 32);
       const uint32_t dk_lo = (uint32_t)dk, dk_hi = (uint32_t)(dk >> 32);
@@ -326,14 +337,16 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         PrefillItem rec;
         if (take_item(item_no, rec) < 0) break;
         const int n_tiles = rec.n_tiles;
-        const int qb = item_no & 1u;
-        mbar_wait_bounded(&sm.q_full[qb], (item_no >> 1) & 1u, abort_flag, p.status);
-        const uint32_t q_lo = dq_lo + (uint32_t)((qb * kTcQBytes) >> 4);
+        mbar_wait_bounded(&sm.q_full, item_no & 1u, abort_flag, p.status);
+        const uint32_t q_lo = dq_lo;
+        if (n_tiles == 0) umma_commit(&sm.q_empty);
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
           const int s = it % kTcKStages;
-          const int b = it % kTcSBufs;
+          const int b = it & 1u;
           mbar_wait_bounded(&sm.k_full[s], (it / kTcKStages) & 1u, abort_flag, p.status);
-          mbar_wait_bounded(&sm.s_empty[b], ((it / kTcSBufs) & 1u) ^ 1u, abort_flag, p.status);
+          PF_TRACE(13, it);
+          mbar_wait_bounded(&sm.s_empty[b], ((it >> 1) & 1u) ^ 1u, abort_flag, p.status);
+          PF_TRACE(15, it);
           tc_fence_after();
           const uint32_t k_lo = dk_lo + (uint32_t)((s * kPfTileBytes) >> 4);
           const uint32_t d_tmem = tmem + b * 128;
@@ -347,9 +360,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           }
           umma_commit(&sm.s_full[b]);
           umma_commit(&sm.k_empty[s]);
+          if (tile == n_tiles - 1) umma_commit(&sm.q_empty);   // the Q buffer may be refilled
           PF_TRACE(4, it);
         }
-        umma_commit(&sm.q_empty[qb]);          // the Q buffer may be refilled once these MMAs have run
       }
     }
     __syncwarp();
@@ -367,14 +380,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         for (int tile = 0; tile < n_tiles; ++tile, ++it) {
           const int s = it % kTcVStages;
           const int g = it & 1u;                            // the group that owns this tile
-          const int b = it % kTcSBufs;
           mbar_wait_bounded(&sm.v_full[s], (it / kTcVStages) & 1u, abort_flag, p.status);
           mbar_wait_bounded(&sm.p_full[g], (it >> 1) & 1u, abort_flag, p.status);
           tc_fence_after();
           PF_TRACE(5, it);
           const uint32_t v_lo = dv_lo + (uint32_t)((s * kPfTileBytes) >> 4);
-          // P of the tile: bf16 pairs in the last 64 columns of its S buffer
-          const uint32_t p_tmem = tmem + b * 128 + 64;
+          const uint32_t p_tmem = tmem + kTcPCol + g * 64;  // P of the tile: 128 tokens as bf16 pairs
           const uint32_t d_tmem = tmem + kTcOCol;
           if (tile == 0)                                    // the first tile of the item overwrites
             umma_bf16_ts_lo<false>(d_tmem, p_tmem, v_lo, dv_hi, idesc_pv);
@@ -385,7 +396,6 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             umma_bf16_ts_lo<true>(d_tmem, p_tmem + ks * 8, v_lo + (uint32_t)((ks * 2048) >> 4), dv_hi, idesc_pv);
           umma_commit(&sm.pv_done[g]);
           umma_commit(&sm.v_empty[s]);
-          umma_commit(&sm.s_empty[b]);                      // S buffer (and the P inside it) may be overwritten
           PF_TRACE(6, it);
         }
         umma_commit(&sm.o_done);
@@ -398,6 +408,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     const int r = threadIdx.x & 127;                 // query row of the tile == TMEM lane
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     const uint32_t o_col = lane_base + kTcOCol;
+    const uint32_t p_col = lane_base + kTcPCol + g * 64;
     const int G = p.group;
     uint32_t it = 0;
     for (uint32_t item_no = 0;; ++item_no) {
@@ -413,18 +424,15 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       float l = 0.f;
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
         if ((int)(it & 1u) != g) continue;             // the other group's tile
-        const uint32_t sb = it % kTcSBufs;
-        const uint32_t s_col = lane_base + sb * 128;   // P aliases the second half of the buffer
-        if (r == 0) PF_TRACE(0 + g * 10, it);
-        mbar_wait_bounded(&sm.s_full[sb], (it / kTcSBufs) & 1u, abort_flag, p.status);
+        const uint32_t sb = it & 1u;
+        const uint32_t s_col = lane_base + sb * 128;
+        if (r == 0) PF_TRACE(0, it);
+        mbar_wait_bounded(&sm.s_full[sb], (it >> 1) & 1u, abort_flag, p.status);
         tc_fence_after();
-        if (r == 0) PF_TRACE(1 + g * 10, it);
+        if (r == 0) PF_TRACE(1, it);
         const int tbase = tile * kPfTile;
         const bool need_mask = tbase + kPfTile - 1 > lim;
-        auto load_half = [&](int half, uint32_t (&sr)[2][32]) {
-          tmem_ld32(s_col + half * 64, sr[0]);
-          tmem_ld32(s_col + half * 64 + 32, sr[1]);
-          tmem_wait_ld();
+        auto mask_half = [&](int half, uint32_t (&sr)[2][32]) {
           if (need_mask) {
 #pragma unroll
             for (int h = 0; h < 2; ++h)
@@ -432,6 +440,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
               for (int c = 0; c < 32; ++c)
                 if (tbase + half * 64 + h * 32 + c > lim) sr[h][c] = __float_as_uint(-INFINITY);
           }
+        };
+        auto load_half = [&](int half, uint32_t (&sr)[2][32]) {
+          tmem_ld32(s_col + half * 64, sr[0]);
+          tmem_ld32(s_col + half * 64 + 32, sr[1]);
+          tmem_wait_ld();
+          mask_half(half, sr);
         };
         auto max_half = [&](const uint32_t (&sr)[2][32]) -> float {
           float mq[8];                      // eight independent chains instead of one of 64
@@ -460,6 +474,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         const float m_used = rescale ? fmaxf(m_in, mx) : m_in;
         sm.row_ms[it & 1u][r] = m_used;
         mbar_arrive(&sm.m_ready[it & 1u]);             // release: the next tile's owner may go on
+        if (r == 0) PF_TRACE(11, it);
         const float corr = (!rescale) ? 1.f : (m_in == -INFINITY ? 0.f : fast_exp2((m_in - m_used) * p.scale_log2));
         if (m_used != m_ref) {                         // bring this group's row sum to the new reference
           l *= (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_used) * p.scale_log2);
@@ -480,20 +495,25 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         };
         // pass 2: probabilities of the second half (already in registers), then the first
-        // half again.  P (128 tokens, bf16 pairs) goes to the second half of the S buffer,
-        // which is free as soon as its values are in registers.
-        uint32_t pk[32];
-        exp_half(sr, pk);
-        tmem_st32(s_col + 96, pk);
+        // half again; the S buffer goes back to the MMA issuer as soon as that is loaded
+        uint32_t pk_hi[32], pk_lo[32];
+        exp_half(sr, pk_hi);
         load_half(0, sr);
-        exp_half(sr, pk);
-        tmem_st32(s_col + 64, pk);
-        if (r == 0) PF_TRACE(2 + g * 10, it);
-        // O may be touched once the previous tile's P V is done (rare path).  The barrier of
-        // that tile's parity has completed (it - 1) / 2 or (it - 1) / 2 + 1 phases here: the S
-        // just read could only be computed after the P V of tile it - 3 had run.
+        tc_fence_before();
+        mbar_arrive(&sm.s_empty[sb]);
+        if (r == 0) PF_TRACE(10, it);
+        exp_half(sr, pk_lo);
+        if (r == 0) PF_TRACE(2, it);
+        // The group's P buffer is free once its previous tile's P V has run.  Every P V up
+        // to tile it - 4 is known to be done (this group waited for it two tiles ago, or the
+        // previous item's epilogue did), so the parity wait cannot be off by a phase.
+        if (tile >= 2) {
+          mbar_wait_bounded(&sm.pv_done[g], ((it - 2) >> 1) & 1u, abort_flag, p.status);
+          tc_fence_after();
+        }
+        // O may be touched once the previous tile's P V (the other group's) has run: rare path
         if (rescale && tile > 0) {
-          mbar_wait_bounded(&sm.pv_done[(it - 1) & 1u], ((it - 1) >> 1) & 1u, abort_flag, p.status);
+          mbar_wait_bounded(&sm.pv_done[g ^ 1], ((it - 1) >> 1) & 1u, abort_flag, p.status);
           tc_fence_after();
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
@@ -505,10 +525,13 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             tmem_st32(o_col + c * 32, orow);
           }
         }
+        if (r == 0) PF_TRACE(12, it);
+        tmem_st32(p_col, pk_lo);
+        tmem_st32(p_col + 32, pk_hi);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_full[g]);
-        if (r == 0) PF_TRACE(3 + g * 10, it);
+        if (r == 0) PF_TRACE(3, it);
       }
       if (r == 0 && g == 0) PF_TRACE(7, it > 0 ? it - 1 : 0);
       // ---- merge the groups' row sums and write the item: group g writes columns [64 g, 64 g + 64)
@@ -527,65 +550,48 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       {
         const float lsum = sm.row_l[0][r] + sm.row_l[1][r];
         const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        if (p.out_is_f32) {
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            const int col = g * 64 + c * 32;
-            uint32_t o[32];
-            tmem_ld32(o_col + col, o);
-            tmem_wait_ld();
-            if (valid) {
-              float* dst = reinterpret_cast<float*>(p.out) + (tok * p.num_q_heads + head) * kPfHeadDim + col;
+        for (int c = 0; c < 2; ++c) {
+          const int col = g * 64 + c * 32;
+          uint32_t o[32];
+          if (r == 0 && g == 0) PF_TRACE(0 + c * 3, 95 - item_no);
+          tmem_ld32(o_col + col, o);
+          tmem_wait_ld();
+          if (r == 0 && g == 0) PF_TRACE(1 + c * 3, 95 - item_no);
+          if (!(lsum > 0.f)) {               // no visible key: zeros, whatever the accumulator holds
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (valid) {
+            const int64_t off = (tok * p.num_q_heads + head) * kPfHeadDim + col;
+            if (p.out_is_f32) {
+              float* dst = reinterpret_cast<float*>(p.out) + off;
 #pragma unroll
               for (int i = 0; i < 32; i += 4)
                 *reinterpret_cast<float4*>(dst + i) =
                     make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
                                 __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            }
-          }
-        } else {
-          // bf16 rows go through the item's Q buffer (all its MMAs have run): 128 rows of
-          // 256 B, 16-byte chunks XOR-swizzled by the row, then out in whole 256-byte rows
-          uint8_t* stage = sm.q[item_no & 1u];
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            uint32_t o[32];
-            tmem_ld32(o_col + g * 64 + c * 32, o);
-            tmem_wait_ld();
+            } else {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uint4 v;
-              v.x = pack_bf16(__uint_as_float(o[8 * j]) * inv, __uint_as_float(o[8 * j + 1]) * inv);
-              v.y = pack_bf16(__uint_as_float(o[8 * j + 2]) * inv, __uint_as_float(o[8 * j + 3]) * inv);
-              v.z = pack_bf16(__uint_as_float(o[8 * j + 4]) * inv, __uint_as_float(o[8 * j + 5]) * inv);
-              v.w = pack_bf16(__uint_as_float(o[8 * j + 6]) * inv, __uint_as_float(o[8 * j + 7]) * inv);
-              const int ch = g * 8 + c * 4 + j;
-              *reinterpret_cast<uint4*>(stage + r * 256 + ((ch ^ (r & 15)) << 4)) = v;
+              for (int i = 0; i < 32; i += 8) {
+                uint4 v;
+                v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+                v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                *reinterpret_cast<uint4*>(dst + i) = v;
+              }
             }
           }
-          named_bar_sync(1, kTcSoftmaxThreads);
-          const int ch = lane & 15;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int row = warp * 16 + 2 * i + (lane >> 4);
-            const int rgo = item.row0 + row;
-            if (rgo < rows_total) {
-              const uint4 v = *reinterpret_cast<const uint4*>(stage + row * 256 + ((ch ^ (row & 15)) << 4));
-              const int64_t t = item.q_start + rgo / G;
-              const int h = item.kv_head * G + rgo % G;
-              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) +
-                                        (t * p.num_q_heads + h) * kPfHeadDim + ch * 8) = v;
-            }
-          }
-          fence_proxy_async_smem();      // the buffer is refilled by TMA next
+          if (r == 0 && g == 0) PF_TRACE(2 + c * 3, 95 - item_no);
         }
-        mbar_arrive(&sm.q_empty[item_no & 1u]);
         if (valid && p.lse_out && g == 0)
           p.lse_out[tok * p.num_q_heads + head] = lsum > 0.f ? mm * p.scale + __logf(lsum) : -INFINITY;
       }
+      if (r == 0 && g == 0) PF_TRACE(6, 95 - item_no);
       // nobody may start the next item (new Q, new P V into O) while the other
       // group still reads this item's accumulators or row state
-      if (r == 0 && g == 0) PF_TRACE(15, it > 0 ? it - 1 : 0);
       tc_fence_before();
       named_bar_sync(1, kTcSoftmaxThreads);
       if (r == 0 && g == 0) PF_TRACE(8, it > 0 ? it - 1 : 0);
