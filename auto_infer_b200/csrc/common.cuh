@@ -100,10 +100,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // wait gives up, raises the CTA-wide abort flag (every later wait in the CTA
 // then returns at once, so control flow stays uniform and the kernel drains to
 // its end) and records B200_STATUS_WAIT_TIMEOUT for the host.
-__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* cta_abort, int32_t* status,
-                                                  uint64_t limit_ns = 2000000000ull) {
-  if (mbar_try_wait(bar, parity)) return;
+// The spinning part lives in one out-of-line copy: the kernels have dozens of wait sites
+// and their instruction footprint matters more than a call on the slow path.  A kernel that
+// moves registers between its warps (setmaxnreg) cannot contain calls: its translation unit
+// defines B200_INLINE_WAITS before including this header.
+#ifdef B200_INLINE_WAITS
+static __device__ __forceinline__ void mbar_wait_slow(
+#else
+static __device__ __noinline__ void mbar_wait_slow(
+#endif
+    uint64_t* bar, uint32_t parity, volatile int* cta_abort,
+                                            int32_t* status, uint64_t limit_ns) {
   const uint64_t t0 = global_timer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
@@ -116,6 +123,12 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity
       }
     }
   }
+}
+__device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  volatile int* cta_abort, int32_t* status,
+                                                  uint64_t limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return;
+  mbar_wait_slow(bar, parity, cta_abort, status, limit_ns);
 }
 
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {

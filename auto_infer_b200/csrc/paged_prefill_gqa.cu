@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <vector>
 
+#define B200_INLINE_WAITS
 #include "common.cuh"
 #include "decode_plan.h"
 #include "tc05.cuh"
@@ -95,9 +96,14 @@ struct PrefillParams {
 // ============================================================================
 constexpr int kTcKStages = 3;             // 32 KB per stage
 constexpr int kTcVStages = 3;
-constexpr int kTcKLead = 1;               // K loads run this many tiles ahead of the V loads
+#ifndef B200_PF_KLEAD
+#define B200_PF_KLEAD 1
+#endif
+constexpr int kTcKLead = B200_PF_KLEAD;   // K loads run this many tiles ahead of the V loads
 constexpr int kTcSoftmaxThreads = 256;
-constexpr int kTcThreads = kTcSoftmaxThreads + 96;
+constexpr int kTcThreads = kTcSoftmaxThreads + 128;   // three role warps and a spare one: whole warpgroups
+constexpr int kTcRegsSoftmax = 232;       // after the register hand-over below (8 warps)
+constexpr int kTcRegsOther = 40;          // (4 warps); 256 * 232 + 128 * 40 = 384 * 168
 constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O [256,384) P_A [384,448) P_B [448,512)
 constexpr int kTcOCol = 256;
 constexpr int kTcPCol = 384;
@@ -174,6 +180,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // The softmax threads keep a whole 128-column score row in registers (reading it from
+  // tensor memory twice cost 13 % of the kernel); the warps that only issue TMA loads and
+  // MMAs give them the registers for it (setmaxnreg below, executed by whole warpgroups).
   grid_dep_wait();                // q and the step's new cache rows come from earlier kernels
   const uint32_t tmem = sm.tmem_base;
   volatile int* abort_flag = &sm.abort_flag;
@@ -190,6 +199,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     return (*abort_flag || idx < 0 || idx >= p.num_items) ? -1 : idx;
   };
 
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcRegsOther));
   if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -235,28 +246,24 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             mbar_arrive(&sm.q_full);
           }
         } else {
-          // lane l copies rows l, l+32, ... (zero for unused rows)
+          // lane l copies rows l, l+32, ... (zero for unused rows), four 16-byte chunks in
+          // flight: this warp runs on few registers
           const int rows_total = item.q_len * p.group;
 #pragma unroll 1
-          for (int rr = 0; rr < kPfRows; rr += 64) {
-            uint4 v[2][16];
+          for (int r = lane; r < kPfRows; r += 32) {
+            const int rg = item.row0 + r;
+            const bool valid = rg < rows_total;
+            const uint4* src = reinterpret_cast<const uint4*>(
+                p.q + (int64_t)(item.q_start + (valid ? rg / p.group : 0)) * p.q_stride +
+                (int64_t)(item.kv_head * p.group + (valid ? rg % p.group : 0)) * kPfHeadDim);
+#pragma unroll 1
+            for (int c0 = 0; c0 < 16; c0 += 4) {
+              uint4 v[4];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int r = rr + h * 32 + lane;
-              const int rg = item.row0 + r;
-              const bool valid = rg < rows_total;
-              const uint4* src = reinterpret_cast<const uint4*>(
-                  p.q + (int64_t)(item.q_start + (valid ? rg / p.group : 0)) * p.q_stride +
-                  (int64_t)(item.kv_head * p.group + (valid ? rg % p.group : 0)) * kPfHeadDim);
+              for (int c = 0; c < 4; ++c) v[c] = valid ? __ldg(src + c0 + c) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-              for (int c = 0; c < 16; ++c) v[h][c] = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
-            }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int r = rr + h * 32 + lane;
-#pragma unroll
-              for (int c = 0; c < 16; ++c)
-                *reinterpret_cast<uint4*>(sm.q + (c >> 3) * (kPfRows * 128) + swz128(r, c & 7)) = v[h][c];
+              for (int c = 0; c < 4; ++c)
+                *reinterpret_cast<uint4*>(sm.q + ((c0 + c) >> 3) * (kPfRows * 128) + swz128(r, (c0 + c) & 7)) = v[c];
             }
           }
           fence_proxy_async_smem();
@@ -402,7 +409,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       }
     }
     __syncwarp();
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTcRegsSoftmax));
     // --------------------------- softmax + epilogue ---------------------------
     const int g = warp >> 2;                         // group: KV tiles whose running index & 1 == g
     const int r = threadIdx.x & 127;                 // query row of the tile == TMEM lane
@@ -432,36 +441,32 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         if (r == 0) PF_TRACE(1, it);
         const int tbase = tile * kPfTile;
         const bool need_mask = tbase + kPfTile - 1 > lim;
-        auto mask_half = [&](int half, uint32_t (&sr)[2][32]) {
-          if (need_mask) {
+        // The whole score row goes to registers in one go and the S buffer straight back to
+        // the MMA issuer.
+        uint32_t sv[4][32];
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
+        for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(s_col + q4 * 32, sv[q4]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&sm.s_empty[sb]);
+        if (r == 0) PF_TRACE(10, it);
+        if (need_mask) {
 #pragma unroll
-              for (int c = 0; c < 32; ++c)
-                if (tbase + half * 64 + h * 32 + c > lim) sr[h][c] = __float_as_uint(-INFINITY);
-          }
-        };
-        auto load_half = [&](int half, uint32_t (&sr)[2][32]) {
-          tmem_ld32(s_col + half * 64, sr[0]);
-          tmem_ld32(s_col + half * 64 + 32, sr[1]);
-          tmem_wait_ld();
-          mask_half(half, sr);
-        };
-        auto max_half = [&](const uint32_t (&sr)[2][32]) -> float {
-          float mq[8];                      // eight independent chains instead of one of 64
+          for (int q4 = 0; q4 < 4; ++q4)
 #pragma unroll
-          for (int u = 0; u < 8; ++u) mq[u] = __uint_as_float(sr[0][u]);
+            for (int c = 0; c < 32; ++c)
+              if (tbase + q4 * 32 + c > lim) sv[q4][c] = __float_as_uint(-INFINITY);
+        }
+        float mx;
+        {
+          float mq[8];                      // eight independent chains instead of one of 128
 #pragma unroll
-          for (int c = 8; c < 64; ++c) mq[c & 7] = fmaxf(mq[c & 7], __uint_as_float(sr[c >> 5][c & 31]));
-          return fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])),
-                       fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
-        };
-        // pass 1: row maximum over the tile's 128 columns (second half stays in registers)
-        uint32_t sr[2][32];
-        load_half(0, sr);
-        float mx = max_half(sr);
-        load_half(1, sr);
-        mx = fmaxf(mx, max_half(sr));
+          for (int u = 0; u < 8; ++u) mq[u] = __uint_as_float(sv[0][u]);
+#pragma unroll
+          for (int c = 8; c < 128; ++c) mq[c & 7] = fmaxf(mq[c & 7], __uint_as_float(sv[c >> 5][c & 31]));
+          mx = fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])),
+                     fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
+        }
         // the maximum O is scaled to after the previous tile (owned by the other group)
         float m_in = -INFINITY;
         if (tile > 0) {
@@ -475,35 +480,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         sm.row_ms[it & 1u][r] = m_used;
         mbar_arrive(&sm.m_ready[it & 1u]);             // release: the next tile's owner may go on
         if (r == 0) PF_TRACE(11, it);
-        const float corr = (!rescale) ? 1.f : (m_in == -INFINITY ? 0.f : fast_exp2((m_in - m_used) * p.scale_log2));
         if (m_used != m_ref) {                         // bring this group's row sum to the new reference
           l *= (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - m_used) * p.scale_log2);
           m_ref = m_used;
         }
         const float ms = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
-        auto exp_half = [&](const uint32_t (&sr)[2][32], uint32_t (&pk)[32]) {
-          float ls[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(sr[h][c]), p.scale_log2, -ms));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(sr[h][c + 1]), p.scale_log2, -ms));
-              ls[(c >> 1) & 3] += p0 + p1;
-              pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
-            }
-          l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-        };
-        // pass 2: probabilities of the second half (already in registers), then the first
-        // half again; the S buffer goes back to the MMA issuer as soon as that is loaded
-        uint32_t pk_hi[32], pk_lo[32];
-        exp_half(sr, pk_hi);
-        load_half(0, sr);
-        tc_fence_before();
-        mbar_arrive(&sm.s_empty[sb]);
-        if (r == 0) PF_TRACE(10, it);
-        exp_half(sr, pk_lo);
-        if (r == 0) PF_TRACE(2, it);
         // The group's P buffer is free once its previous tile's P V has run.  Every P V up
         // to tile it - 4 is known to be done (this group waited for it two tiles ago, or the
         // previous item's epilogue did), so the parity wait cannot be off by a phase.
@@ -513,6 +494,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         }
         // O may be touched once the previous tile's P V (the other group's) has run: rare path
         if (rescale && tile > 0) {
+          const float corr = (m_in == -INFINITY) ? 0.f : fast_exp2((m_in - m_used) * p.scale_log2);
           mbar_wait_bounded(&sm.pv_done[g ^ 1], ((it - 1) >> 1) & 1u, abort_flag, p.status);
           tc_fence_after();
 #pragma unroll 1
@@ -525,9 +507,24 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             tmem_st32(o_col + c * 32, orow);
           }
         }
-        if (r == 0) PF_TRACE(12, it);
-        tmem_st32(p_col, pk_lo);
-        tmem_st32(p_col + 32, pk_hi);
+        // probabilities, 64 columns at a time: P (bf16 pairs) to the group's buffer
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+              const float p0 = fast_exp2(fmaf(__uint_as_float(sv[half * 2 + h][c]), p.scale_log2, -ms));
+              const float p1 = fast_exp2(fmaf(__uint_as_float(sv[half * 2 + h][c + 1]), p.scale_log2, -ms));
+              ls[(c >> 1) & 3] += p0 + p1;
+              pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
+            }
+          tmem_st32(p_col + half * 32, pk);
+        }
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        if (r == 0) PF_TRACE(2, it);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.p_full[g]);

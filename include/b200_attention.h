@@ -146,7 +146,9 @@ int b200_paged_decode_gqa(const void* q, int64_t q_stride,
  * workspace (this kernel needs none).  plan_dev is not const: two of its header
  * words serve as the kernel's work-queue counters and are back at zero when the
  * kernel ends, so one plan serves all layers of a step as long as the calls that
- * share it do not overlap on the GPU. */
+ * share it do not overlap on the GPU.  q, out and plan_dev must be 16-byte
+ * aligned and q_stride a multiple of 8 elements (B200_EALIGN otherwise); q must
+ * hold at least info->num_tokens rows. */
 typedef struct b200_prefill_plan_info {
   int32_t num_items;       /* 128-row work items                               */
   int32_t total_tiles;     /* 128-token KV tiles summed over the items          */

@@ -49,6 +49,20 @@ def test_chunk_over_prefix_shapes(q_len, prefix):
     torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
 
 
+@pytest.mark.parametrize("n_q,n_kv", [(4, 4), (16, 2), (6, 2), (12, 2)])
+def test_group_sizes(n_q, n_kv):
+    """Groups that divide 128 take the Q tile as one TMA box (1, 8), the others
+    (3, 6) copy it row by row; ragged tails in both."""
+    from auto_infer_b200 import synth
+    b = synth.build_gqa_batch("groups", [(150, 150 + 200), (45, 45), (3, 130)], n_q, n_kv, 128, 24, 911 + n_q)
+    ref, ref_lse = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table,
+                                       b.cu_seqlens_q, b.seqlens_kv, b.scale, return_lse=True)
+    out, lse = _prefill(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                        b.seqlens_kv, b.scale, b.n_q, b.n_kv, want_lse=True)
+    torch.testing.assert_close(out.float(), ref.float(), **TOL)
+    torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
+
+
 def test_mixed_batch_through_the_backend():
     """Decode rows and prefill chunks in one step, as the scheduler orders them
     (decode first): the backend sends each row to the kernel built for it and the
