@@ -32,6 +32,17 @@ struct PrefillItem {
 };
 static_assert(sizeof(PrefillItem) == kPfItemInts * 4, "item layout");
 
+// The order in which an item walks its KV tiles is free (online softmax), so every item
+// starts at a different tile and wraps around: the row tiles of one (sequence, kv head)
+// pair run on different SMs at the same time, and walking in step they would all ask the
+// L2 for the same lines at the same moment.
+#ifndef B200_PF_ROT
+#define B200_PF_ROT 5
+#endif
+__device__ __forceinline__ int first_tile(const PrefillItem& item) {
+  return item.n_tiles > 0 ? ((item.row0 / kPfRows) * B200_PF_ROT) % item.n_tiles : 0;
+}
+
 struct PrefillParams {
   const __nv_bfloat16* q;
   int64_t q_stride;
@@ -65,45 +76,47 @@ struct PrefillParams {
 
 // ============================================================================
 // One 128-row query tile per work item, S and O accumulated in tensor memory by
-// tcgen05.mma.  Warp roles (352 threads, one CTA per SM):
+// tcgen05.mma.  Warp roles (512 threads = four warpgroups, one CTA per SM):
 //   warps 0-3   softmax group A     thread r owns query row r (TMEM lane r)
 //   warps 4-7   softmax group B     same rows, the other half of the KV tiles
-//   warp  8     TMA producer of 64-token K and V tiles (separate rings)
+//   warp  8     TMA producer: Q tile, 128-token K and V tiles (separate rings), work queue
 //   warp  9     tensor-memory owner, issues S = Q K^T
-//   warp  10    issues O += P V
-// 128-token KV tile j of the running sequence belongs to group j & 1 and uses S
-// buffer j & 1: S_j = Q K_j^T (M 128, N 128, 8 x K16) lands there, the group's
-// threads read their row with tcgen05.ld (a thread holds a whole row: no
-// shuffles), hand the buffer back as soon as its values are in registers, and
-// write P as packed bf16 into a tensor-memory buffer of its own; the MMA reads it
-// from there as its A operand: O (+)= P V_j (M 128, N 128, 8 x K16, V read
-// MN-major from the TMA tile).  Both groups accumulate into ONE O under ONE
-// running maximum per row, handed from the owner of tile j to the owner of tile
-// j + 1 through shared memory right after the row maximum of tile j is known, so
-// the groups run half a tile out of phase: while one is in its exponentials (the
-// MUFU floor of the kernel) the other loads, stores or reduces.  Each group keeps
-// its own row sum; the sums are merged at the end of an item.
-// Measured on the part: an M 128 x N 128 x K 16 MMA takes 67 cycles with both
-// operands in shared memory (8 KB read: all the bandwidth an SM has) and 100 cycles
-// with A in tensor memory whatever N <= 128 is, so S = Q K^T keeps Q in shared
-// memory and only P, which the threads produce in registers anyway, goes through
-// tensor memory (two buffers, one per group).
-// The MMAs are queued by two dedicated threads.  O is rescaled in tensor memory
-// only when a row maximum grows by more than 2^8 (the stale maximum is kept
-// otherwise).
+//   warp  10    issues O += P V          (warp 11 only completes the warpgroup)
+//   warps 12-15 epilogue: thread e takes row e of O out of tensor memory and stores it
+// After set-up the warpgroups trade registers (setmaxnreg): 200 per softmax thread, which
+// holds a whole 128-column score row, 40 / 72 for the others.
+// The s-th KV tile an item works on (running count over the CTA's items) belongs to group
+// s & 1 and uses S buffer s & 1: S = Q K^T (M 128, N 128, 8 x K16, both operands in shared
+// memory) lands there, the group's threads read their row with tcgen05.ld (a thread holds a
+// whole row: no shuffles), hand the buffer straight back, and write P as packed bf16 into
+// the group's own P buffer in tensor memory; the MMA reads it from there as its A operand:
+// O (+)= P V (M 128, N 128, 8 x K16, V read MN-major from the TMA tile).  Both groups
+// accumulate into ONE O under ONE running maximum per row, handed from the owner of one
+// step to the owner of the next through shared memory right after the row maximum is
+// known.  Each group keeps its own row sum; the sums are merged by the epilogue warps,
+// which work on item k while the softmax groups are already in item k + 1 (the P V issuer
+// waits for them before it overwrites O).  O is rescaled in tensor memory only when a row
+// maximum grows by more than 2^8 (the stale maximum is kept otherwise).
+// Measured on the part: an M 128 x N 128 x K 16 MMA takes 67 cycles with both operands in
+// shared memory (8 KB read: all the bandwidth an SM has) and 100 cycles with A in tensor
+// memory whatever N <= 128 is, so Q stays in shared memory and only P, which the threads
+// produce in registers anyway, goes through tensor memory.
 // N = 128 per MMA on purpose: a tcgen05.mma costs ~50 cycles to issue whatever its
 // size, so N = 64 instructions (32 cycles of math) would leave the pipe waiting.
 // ============================================================================
 constexpr int kTcKStages = 3;             // 32 KB per stage
 constexpr int kTcVStages = 3;
 #ifndef B200_PF_KLEAD
-#define B200_PF_KLEAD 1
+#define B200_PF_KLEAD 2
 #endif
 constexpr int kTcKLead = B200_PF_KLEAD;   // K loads run this many tiles ahead of the V loads
 constexpr int kTcSoftmaxThreads = 256;
-constexpr int kTcThreads = kTcSoftmaxThreads + 128;   // three role warps and a spare one: whole warpgroups
-constexpr int kTcRegsSoftmax = 232;       // after the register hand-over below (8 warps)
-constexpr int kTcRegsOther = 40;          // (4 warps); 256 * 232 + 128 * 40 = 384 * 168
+constexpr int kTcEpilogueThreads = 128;
+constexpr int kTcThreads = kTcSoftmaxThreads + 128 + kTcEpilogueThreads;   // whole warpgroups: 512 = 4 x 128
+// registers per thread after the hand-over below: 256 * 200 + 128 * 40 + 128 * 72 = 512 * 128
+constexpr int kTcRegsSoftmax = 200;
+constexpr int kTcRegsOther = 40;
+constexpr int kTcRegsEpilogue = 72;
 constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O [256,384) P_A [384,448) P_B [448,512)
 constexpr int kTcOCol = 256;
 constexpr int kTcPCol = 384;
@@ -113,7 +126,8 @@ struct __align__(1024) TcSmem {
   uint8_t q[kTcQBytes];                    // [dim half][128 rows][128 B], swizzled
   uint8_t k[kTcKStages][kPfTileBytes];     // [dims 0-63 | dims 64-127], 128 tokens x 128 B each
   uint8_t v[kTcVStages][kPfTileBytes];
-  float row_l[2][kPfRows];                 // end-of-item exchange of the groups' row sums
+  float row_l[2][kPfRows];                 // end of item: the groups' row sums, scaled to the final maximum
+  float row_mfin[kPfRows];                 // end of item: the final row maximum
   float row_ms[2][kPfRows];                // running row maximum after tile j, slot j & 1
   uint64_t k_full[kTcKStages];
   uint64_t k_empty[kTcKStages];
@@ -124,7 +138,10 @@ struct __align__(1024) TcSmem {
   uint64_t p_full[2];                      // per group
   uint64_t pv_done[2];                     // per tile parity
   uint64_t m_ready[2];                     // per tile parity: row_ms[parity] is written
-  uint64_t o_done;
+  uint64_t o_done;                         // P V issuer -> epilogue warps: the item's O is complete
+  uint64_t o_free;                         // epilogue warps -> P V issuer: O is in registers
+  uint64_t l_full;                         // softmax threads -> epilogue warps: row_l / row_mfin written
+  uint64_t l_empty;                        // and read
   uint64_t q_full;                         // producer warp: the item's Q tile is staged
   uint64_t q_empty;                        // all S MMAs of the item have run
   uint64_t item_full[2];                   // work-queue hand-off: producer warp -> the other roles
@@ -166,9 +183,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       mbar_init(&sm.pv_done[b], 1);
       mbar_init(&sm.m_ready[b], 128);
       mbar_init(&sm.item_full[b], 1);
-      mbar_init(&sm.item_empty[b], kTcSoftmaxThreads + 2);   // softmax threads + the two MMA threads
+      mbar_init(&sm.item_empty[b], kTcSoftmaxThreads + 2 + kTcEpilogueThreads);   // all consumers of the mailbox
     }
     mbar_init(&sm.o_done, 1);
+    mbar_init(&sm.o_free, kTcEpilogueThreads);
+    mbar_init(&sm.l_full, kTcSoftmaxThreads);
+    mbar_init(&sm.l_empty, kTcEpilogueThreads);
     mbar_init(&sm.q_full, 32);
     mbar_init(&sm.q_empty, 1);
     mbar_fence_init();
@@ -199,7 +219,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     return (*abort_flag || idx < 0 || idx >= p.num_items) ? -1 : idx;
   };
 
-  if (warp >= 8) {
+  if (warp >= 8 && warp < 12) {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcRegsOther));
   if (warp == 8) {
     // ------------------------------ TMA producer ------------------------------
@@ -275,8 +295,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       // S = Q K^T has run, long before the V stage of the same tile (held until P V has
       // run).  So the K loads run kTcKLead tiles ahead of the V loads: a full V ring does
       // not keep the next K, which the S MMA needs first, from being requested.
-      auto issue = [&](bool is_k, int tile, uint32_t itx) {
+      const int rot = first_tile(item);
+      auto issue = [&](bool is_k, int step, uint32_t itx) {
         int bid = 0;
+        int tile = step + rot;
+        if (tile >= item.n_tiles) tile -= item.n_tiles;
         const int token0 = tile * kPfTile + lane * p.box_tokens;     // first token of this lane's box
         if (lane < nbox) {
           int lb = token0 >> p.block_shift;
@@ -389,6 +412,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           const int g = it & 1u;                            // the group that owns this tile
           mbar_wait_bounded(&sm.v_full[s], (it / kTcVStages) & 1u, abort_flag, p.status);
           mbar_wait_bounded(&sm.p_full[g], (it >> 1) & 1u, abort_flag, p.status);
+          if (tile == 0 && item_no > 0)                     // the previous item's O has been read
+            mbar_wait_bounded(&sm.o_free, (item_no - 1) & 1u, abort_flag, p.status);
           tc_fence_after();
           PF_TRACE(5, it);
           const uint32_t v_lo = dv_lo + (uint32_t)((s * kPfTileBytes) >> 4);
@@ -410,7 +435,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     }
     __syncwarp();
   }
-  } else {
+  } else if (warp < 8) {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kTcRegsSoftmax));
     // --------------------------- softmax + epilogue ---------------------------
     const int g = warp >> 2;                         // group: KV tiles whose running index & 1 == g
@@ -429,6 +454,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       const int64_t tok = item.q_start + (valid ? rg / G : 0);
       const int head = item.kv_head * G + (valid ? rg % G : 0);
       const int lim = valid ? min(item.causal_base + rg / G, item.kv_len - 1) : -1;
+      const int rot = first_tile(item);
       float m_ref = -INFINITY;       // maximum this group's row sum is scaled to
       float l = 0.f;
       for (int tile = 0; tile < item.n_tiles; ++tile, ++it) {
@@ -439,7 +465,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         mbar_wait_bounded(&sm.s_full[sb], (it >> 1) & 1u, abort_flag, p.status);
         tc_fence_after();
         if (r == 0) PF_TRACE(1, it);
-        const int tbase = tile * kPfTile;
+        int kv_tile = tile + rot;                      // the KV tile this step works on
+        if (kv_tile >= item.n_tiles) kv_tile -= item.n_tiles;
+        const int tbase = kv_tile * kPfTile;
         const bool need_mask = tbase + kPfTile - 1 > lim;
         // The whole score row goes to registers in one go and the S buffer straight back to
         // the MMA issuer.
@@ -485,10 +513,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
           m_ref = m_used;
         }
         const float ms = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
-        // The group's P buffer is free once its previous tile's P V has run.  Every P V up
-        // to tile it - 4 is known to be done (this group waited for it two tiles ago, or the
-        // previous item's epilogue did), so the parity wait cannot be off by a phase.
-        if (tile >= 2) {
+        // The group's P buffer is free once the P V of its previous tile (of this item or the
+        // one before) has run.  The group waited for the one before that two tiles ago, so
+        // the parity wait cannot be off by a phase.
+        if (it >= 2) {
           mbar_wait_bounded(&sm.pv_done[g], ((it - 2) >> 1) & 1u, abort_flag, p.status);
           tc_fence_after();
         }
@@ -507,21 +535,27 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             tmem_st32(o_col + c * 32, orow);
           }
         }
-        // probabilities, 64 columns at a time: P (bf16 pairs) to the group's buffer
+        // Probabilities, software-pipelined by a quarter of the row: the exponentials of
+        // quarter q are issued while quarter q - 1 is summed and packed, so nothing waits for a
+        // MUFU result.  P (bf16 pairs) goes to the group's buffer 64 columns at a time.
         float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t pk[32];
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t pk[32];
+        for (int q4 = 0; q4 <= 4; ++q4) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int c = 0; c < 32; c += 2) {
-              const float p0 = fast_exp2(fmaf(__uint_as_float(sv[half * 2 + h][c]), p.scale_log2, -ms));
-              const float p1 = fast_exp2(fmaf(__uint_as_float(sv[half * 2 + h][c + 1]), p.scale_log2, -ms));
-              ls[(c >> 1) & 3] += p0 + p1;
-              pk[h * 16 + (c >> 1)] = pack_bf16(p0, p1);
+          for (int c = 0; c < 32; c += 2) {
+            if (q4 < 4) {
+              sv[q4][c] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sv[q4][c]), p.scale_log2, -ms)));
+              sv[q4][c + 1] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sv[q4][c + 1]), p.scale_log2, -ms)));
             }
-          tmem_st32(p_col + half * 32, pk);
+            if (q4 > 0) {
+              const float p0 = __uint_as_float(sv[q4 - 1][c]), p1 = __uint_as_float(sv[q4 - 1][c + 1]);
+              ls[(c >> 1) & 3] += p0 + p1;
+              pk[((q4 - 1) & 1) * 16 + (c >> 1)] = pack_bf16(p0, p1);
+            }
+          }
+          if (q4 == 2) tmem_st32(p_col, pk);
+          if (q4 == 4) tmem_st32(p_col + 32, pk);
         }
         l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         if (r == 0) PF_TRACE(2, it);
@@ -531,67 +565,81 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         if (r == 0) PF_TRACE(3, it);
       }
       if (r == 0 && g == 0) PF_TRACE(7, it > 0 ? it - 1 : 0);
-      // ---- merge the groups' row sums and write the item: group g writes columns [64 g, 64 g + 64)
+      // ---- hand the row sums to the epilogue warps and go on with the next item
       // the maxima only grow along the tiles: the last tile's is what O is scaled to
       float mm = -INFINITY;
       if (item.n_tiles > 0) {
         mbar_wait_bounded(&sm.m_ready[(it - 1) & 1u], ((it - 1) >> 1) & 1u, abort_flag, p.status);
         mm = sm.row_ms[(it - 1) & 1u][r];
       }
+      if (item_no > 0) mbar_wait_bounded(&sm.l_empty, (item_no - 1) & 1u, abort_flag, p.status);
       sm.row_l[g][r] = (m_ref == -INFINITY) ? 0.f : l * fast_exp2((m_ref - mm) * p.scale_log2);
+      if (g == 0) sm.row_mfin[r] = mm;
+      mbar_arrive(&sm.l_full);
+    }
+  } else {
+    // ------------------------------- epilogue --------------------------------
+    // Thread e owns query row e (TMEM lane e): it takes O out of tensor memory as soon as
+    // the item's last P V has run, frees the accumulator for the next item (whose first
+    // tiles the softmax groups are already working on) and normalises and stores the row.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kTcRegsEpilogue));
+    const int r = threadIdx.x - (kTcThreads - kTcEpilogueThreads);
+    const uint32_t o_col = tmem + ((uint32_t)((warp & 3) * 32) << 16) + kTcOCol;
+    const int G = p.group;
+    for (uint32_t item_no = 0;; ++item_no) {
+      PrefillItem item;
+      if (take_item(item_no, item) < 0) break;
+      const int rg = item.row0 + r;
+      const bool valid = rg < item.q_len * G;
+      const int64_t tok = item.q_start + (valid ? rg / G : 0);
+      const int head = item.kv_head * G + (valid ? rg % G : 0);
+      mbar_wait_bounded(&sm.l_full, item_no & 1u, abort_flag, p.status);
+      const float lsum = sm.row_l[0][r] + sm.row_l[1][r];
+      const float mm = sm.row_mfin[r];
+      mbar_arrive(&sm.l_empty);
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
       mbar_wait_bounded(&sm.o_done, item_no & 1u, abort_flag, p.status);
       tc_fence_after();
-      if (r == 0 && g == 0) PF_TRACE(9, it > 0 ? it - 1 : 0);
-      named_bar_sync(1, kTcSoftmaxThreads);
-      if (r == 0 && g == 0) PF_TRACE(14, it > 0 ? it - 1 : 0);
-      {
-        const float lsum = sm.row_l[0][r] + sm.row_l[1][r];
-        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      if (r == 0) PF_TRACE(9, 95 - item_no);
 #pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          const int col = g * 64 + c * 32;
-          uint32_t o[32];
-          if (r == 0 && g == 0) PF_TRACE(0 + c * 3, 95 - item_no);
-          tmem_ld32(o_col + col, o);
-          tmem_wait_ld();
-          if (r == 0 && g == 0) PF_TRACE(1 + c * 3, 95 - item_no);
-          if (!(lsum > 0.f)) {               // no visible key: zeros, whatever the accumulator holds
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32(o_col + c * 32, o);
+        tmem_wait_ld();
+        if (c == 3) {                        // the whole row is out of tensor memory
+          tc_fence_before();
+          mbar_arrive(&sm.o_free);
+        }
+        if (!(lsum > 0.f)) {                 // no visible key: zeros, whatever the accumulator holds
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = 0u;
-          }
-          if (valid) {
-            const int64_t off = (tok * p.num_q_heads + head) * kPfHeadDim + col;
-            if (p.out_is_f32) {
-              float* dst = reinterpret_cast<float*>(p.out) + off;
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (valid) {
+          const int64_t off = (tok * p.num_q_heads + head) * kPfHeadDim + c * 32;
+          if (p.out_is_f32) {
+            float* dst = reinterpret_cast<float*>(p.out) + off;
 #pragma unroll
-              for (int i = 0; i < 32; i += 4)
-                *reinterpret_cast<float4*>(dst + i) =
-                    make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
-                                __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            } else {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
+            for (int i = 0; i < 32; i += 4)
+              *reinterpret_cast<float4*>(dst + i) =
+                  make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                              __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + off;
 #pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 v;
-                v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-                v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                *reinterpret_cast<uint4*>(dst + i) = v;
-              }
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+              v.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+              v.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+              v.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + i) = v;
             }
           }
-          if (r == 0 && g == 0) PF_TRACE(2 + c * 3, 95 - item_no);
         }
-        if (valid && p.lse_out && g == 0)
-          p.lse_out[tok * p.num_q_heads + head] = lsum > 0.f ? mm * p.scale + __logf(lsum) : -INFINITY;
       }
-      if (r == 0 && g == 0) PF_TRACE(6, 95 - item_no);
-      // nobody may start the next item (new Q, new P V into O) while the other
-      // group still reads this item's accumulators or row state
-      tc_fence_before();
-      named_bar_sync(1, kTcSoftmaxThreads);
-      if (r == 0 && g == 0) PF_TRACE(8, it > 0 ? it - 1 : 0);
+      if (valid && p.lse_out)
+        p.lse_out[tok * p.num_q_heads + head] = lsum > 0.f ? mm * p.scale + __logf(lsum) : -INFINITY;
+      if (r == 0) PF_TRACE(8, 95 - item_no);
     }
   }
   // ---- teardown: everyone is done with tensor memory before it is released
