@@ -104,8 +104,14 @@ struct PrefillParams {
 // N = 128 per MMA on purpose: a tcgen05.mma costs ~50 cycles to issue whatever its
 // size, so N = 64 instructions (32 cycles of math) would leave the pipe waiting.
 // ============================================================================
-constexpr int kTcKStages = 3;             // 32 KB per stage
-constexpr int kTcVStages = 3;
+#ifndef B200_PF_KST
+#define B200_PF_KST 3
+#endif
+#ifndef B200_PF_VST
+#define B200_PF_VST 3
+#endif
+constexpr int kTcKStages = B200_PF_KST;   // 32 KB per stage
+constexpr int kTcVStages = B200_PF_VST;
 #ifndef B200_PF_KLEAD
 #define B200_PF_KLEAD 2
 #endif
@@ -346,10 +352,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
       it += item.n_tiles;
     }
     if (lane == 0) {   // drain: nothing may still be landing when the CTA leaves
+      for (uint32_t k = 0; k < (uint32_t)kTcKStages && k < it; ++k) {
+        const uint32_t j = it - 1 - k;
+        mbar_wait_bounded(&sm.k_full[j % kTcKStages], (j / kTcKStages) & 1u, abort_flag, p.status);
+      }
       for (uint32_t k = 0; k < (uint32_t)kTcVStages && k < it; ++k) {
         const uint32_t j = it - 1 - k;
-        if (k < (uint32_t)kTcKStages)
-          mbar_wait_bounded(&sm.k_full[j % kTcKStages], (j / kTcKStages) & 1u, abort_flag, p.status);
         mbar_wait_bounded(&sm.v_full[j % kTcVStages], (j / kTcVStages) & 1u, abort_flag, p.status);
       }
     }
