@@ -239,7 +239,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     for (uint32_t k = 0;; ++k) {
       int idx = -1;
       if (lane == 0) {
-        idx = atomicAdd(p.work_counter, 1);
+        // the first item of a CTA is its own index (no round trip to the counter before
+        // the first load); the rest of the list is handed out dynamically
+        idx = (k == 0) ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.work_counter, 1);
         if (idx >= p.num_items || *abort_flag) idx = -1;
         mbar_wait_bounded(&sm.item_empty[k & 1u], ((k >> 1) & 1u) ^ 1u, abort_flag, p.status);
         if (idx >= 0) {
