@@ -12,8 +12,33 @@ from . import _lib
 from ._lib import DecodePlanInfo, PrefillPlanInfo
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr(device) -> int:
+    """Raw cudaStream_t of torch's current stream on ``device``."""
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def _on_device(device):
+    """Device guard for a C call; free when ``device`` is already current (the calls
+    of a step all are, and the guard object costs more than the call's own checks)."""
+    if device.index is None or torch.cuda.current_device() == device.index:
+        return _NO_GUARD
+    return torch.cuda.device(device)
 
 
 def _need_cuda(*tensors) -> None:
@@ -81,7 +106,7 @@ def reshape_and_cache(key: torch.Tensor, value: Optional[torch.Tensor],
     if slot_mapping.dtype != torch.int32:
         slot_mapping = slot_mapping.to(torch.int32)
     slot_mapping = slot_mapping.contiguous()
-    with torch.cuda.device(key.device):
+    with _on_device(key.device):
         rc = lib.b200_reshape_and_cache(
             key.data_ptr(), v_ptr, key_cache.data_ptr(), vc_ptr, slot_mapping.data_ptr(),
             t, n_kv, k_dim, v_dim, key.stride(0), v_stride, block_size, num_blocks,
@@ -153,7 +178,7 @@ def paged_decode_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torc
         out = torch.empty(t, n_q, d, dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
     elif not out.is_contiguous():
         raise ValueError("out must be contiguous")
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         rc = lib.b200_paged_decode_gqa(
             q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
             num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
@@ -226,7 +251,7 @@ def mla_decode_absorbed(q_latent: torch.Tensor, latent_cache: torch.Tensor,
     if out is None:
         out = torch.empty(t, h, kv_lora_rank, dtype=torch.float32 if out_f32 else q_latent.dtype,
                           device=q_latent.device)
-    with torch.cuda.device(q_latent.device):
+    with _on_device(q_latent.device):
         rc = lib.b200_mla_decode_absorbed(
             q_latent.data_ptr(), q_latent.stride(0), latent_cache.data_ptr(), num_blocks, block_size,
             block_table.data_ptr(), block_table.stride(0), plan.dev.data_ptr(),
@@ -294,7 +319,7 @@ def paged_prefill_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: tor
         out = torch.empty(t, n_q, d, dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
     elif not out.is_contiguous():
         raise ValueError("out must be contiguous")
-    with torch.cuda.device(q.device):
+    with _on_device(q.device):
         rc = lib.b200_paged_prefill_gqa(
             q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
             num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
@@ -318,7 +343,7 @@ def lse_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor,
         raise ValueError("each part must be contiguous (rows, D) / (rows,)")
     if out is None:
         out = torch.empty(rows, d, dtype=out_dtype, device=o_parts.device)
-    with torch.cuda.device(o_parts.device):
+    with _on_device(o_parts.device):
         rc = lib.b200_lse_combine(
             o_parts.data_ptr(), lse_parts.data_ptr(), o_parts.stride(0), lse_parts.stride(0),
             r, rows, d, out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
@@ -336,7 +361,7 @@ def cp_exchange_combine(local_record: torch.Tensor, recv_ptrs_dev: int, state: t
     is the device address of the array of receive-buffer pointers."""
     _need_cuda(local_record, state, out)
     lib = _lib.load()
-    with torch.cuda.device(local_record.device):
+    with _on_device(local_record.device):
         rc = lib.b200_cp_exchange_combine(
             local_record.data_ptr(), recv_ptrs_dev, state.data_ptr(), rank, world, rows, head_dim,
             out.data_ptr(), 1 if out.dtype == torch.float32 else 0,

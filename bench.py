@@ -430,16 +430,31 @@ def main():
 
     # ---- end to end through the backend call with host buffers -------------
     backend = B200GqaBackend(b.n_q, b.n_kv, b.head_dim, b.scale, 1, device, torch.bfloat16)
-    host = {k: getattr(b, k).cpu().pin_memory() for k in ("q", "k_new", "v_new", "slot_mapping",
-                                                          "block_table")}
-    dev = {k: torch.empty_like(v, device=device) for k, v in host.items()}
+    # The step's inputs live in one pinned staging arena on the host (as an engine's input
+    # stager keeps them) and travel in one copy; the tensors below are views into it.
+    srcs = {k: getattr(b, k).cpu().contiguous() for k in ("q", "k_new", "v_new", "slot_mapping", "block_table")}
+    offs, total = {}, 0
+    for k, v in srcs.items():
+        offs[k] = total
+        total += (v.numel() * v.element_size() + 255) // 256 * 256
+    host_arena = torch.empty(total, dtype=torch.uint8).pin_memory()
+    dev_arena = torch.empty(total, dtype=torch.uint8, device=device)
+
+    def _view(arena, k):
+        v = srcs[k]
+        n = v.numel() * v.element_size()
+        return arena[offs[k]:offs[k] + n].view(v.dtype).view(v.shape)
+
+    host = {k: _view(host_arena, k) for k in srcs}
+    for k in srcs:
+        host[k].copy_(srcs[k])
+    dev = {k: _view(dev_arena, k) for k in srcs}
     out_host = torch.empty(b.q.shape, dtype=torch.bfloat16).pin_memory()
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = out_host.numel() * out_host.element_size()
 
     def e2e_step():
-        for k in host:
-            dev[k].copy_(host[k], non_blocking=True)
+        dev_arena.copy_(host_arena, non_blocking=True)
         if world == 1:
             ctx = ForwardContext(None, None, dev["slot_mapping"], dev["block_table"],
                                  b.cu_seqlens_q, b.seqlens_kv, None, backend, [b.kv_cache], True)

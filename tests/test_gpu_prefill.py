@@ -63,6 +63,28 @@ def test_group_sizes(n_q, n_kv):
     torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
 
 
+def test_two_kernels_agree_on_a_long_context():
+    """Size-independent check at config-5 scale: a decode row is a one-row chunk, so the
+    wide-query kernel (tcgen05, rotated tile order, 1 024 KV tiles per item) and the
+    split-KV decode kernel (mma.sync, tiles cut across CTAs) must give the same rows
+    and the same log-sum-exp for a 131 072-token context."""
+    from auto_infer_b200 import ops, synth
+    b = synth.config5("cuda", batch=2)
+    dplan = ops.DecodePlan(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, "cuda")
+    lse_d = torch.empty(b.q.shape[0], b.n_q, dtype=torch.float32, device="cuda")
+    out_d = ops.paged_decode_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, dplan, b.scale,
+                                 lse_out=lse_d)
+    pplan = ops.PrefillPlan(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, "cuda", min_rows=0)
+    lse_p = torch.empty_like(lse_d)
+    out_p = torch.zeros(b.q.shape, dtype=torch.bfloat16, device="cuda")
+    ops.paged_prefill_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, pplan, b.scale,
+                          out=out_p, lse_out=lse_p)
+    torch.cuda.synchronize()
+    assert ops.read_status("cuda") == 0
+    torch.testing.assert_close(out_p.float(), out_d.float(), atol=4e-3, rtol=2e-2)
+    torch.testing.assert_close(lse_p, lse_d, atol=2e-3, rtol=2e-3)
+
+
 def test_mixed_batch_through_the_backend():
     """Decode rows and prefill chunks in one step, as the scheduler orders them
     (decode first): the backend sends each row to the kernel built for it and the
