@@ -63,6 +63,29 @@ def test_group_sizes(n_q, n_kv):
     torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
 
 
+def test_context_parallel_slice_with_rows_that_see_no_key():
+    """The keys [128, 200) of a 200-token prompt as one context-parallel rank holds them
+    (local block table, local length, causal base in local coordinates): the first 128
+    query positions see none of them, so their work items have no KV tile at all and must
+    come out as zeros with lse = -inf; the others are partial sums for the merge."""
+    from auto_infer_b200 import ops, synth
+    b = synth.build_gqa_batch("cp_slice", [(200, 200)], 8, 2, 128, 8, 4242)
+    ref, ref_lse = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                                       b.seqlens_kv, b.scale, return_lse=True, kv_ranges=[(128, 200)])
+    plan = ops.PrefillPlan(b.cu_seqlens_q, [72], b.n_q, b.n_kv, "cuda", min_rows=0, causal_base=[-128])
+    out = torch.full(b.q.shape, 7.0, dtype=torch.bfloat16, device="cuda")
+    lse = torch.zeros(b.q.shape[0], b.n_q, dtype=torch.float32, device="cuda")
+    local_bt = b.block_table[:, 1:].contiguous().cuda()
+    ops.paged_prefill_gqa(b.q.cuda(), b.kv_cache[0].cuda(), b.kv_cache[1].cuda(), local_bt, plan, b.scale,
+                          out=out, lse_out=lse)
+    torch.cuda.synchronize()
+    assert ops.read_status("cuda") == 0
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **TOL)
+    assert torch.equal(out[:128].cpu(), torch.zeros_like(out[:128].cpu()))
+    assert torch.isinf(lse[:128]).all() and (lse[:128] < 0).all()
+    torch.testing.assert_close(lse[128:].cpu(), ref_lse[128:], atol=2e-3, rtol=2e-3)
+
+
 def test_two_kernels_agree_on_a_long_context():
     """Size-independent check at config-5 scale: a decode row is a one-row chunk, so the
     wide-query kernel (tcgen05, rotated tile order, 1 024 KV tiles per item) and the
