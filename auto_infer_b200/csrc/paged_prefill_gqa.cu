@@ -36,11 +36,9 @@ static_assert(sizeof(PrefillItem) == kPfItemInts * 4, "item layout");
 // starts at a different tile and wraps around: the row tiles of one (sequence, kv head)
 // pair run on different SMs at the same time, and walking in step they would all ask the
 // L2 for the same lines at the same moment.
-#ifndef B200_PF_ROT
-#define B200_PF_ROT 5
-#endif
+constexpr int kPfTileRotation = 5;
 __device__ __forceinline__ int first_tile(const PrefillItem& item) {
-  return item.n_tiles > 0 ? ((item.row0 / kPfRows) * B200_PF_ROT) % item.n_tiles : 0;
+  return item.n_tiles > 0 ? ((item.row0 / kPfRows) * kPfTileRotation) % item.n_tiles : 0;
 }
 
 struct PrefillParams {
@@ -104,18 +102,11 @@ struct PrefillParams {
 // N = 128 per MMA on purpose: a tcgen05.mma costs ~50 cycles to issue whatever its
 // size, so N = 64 instructions (32 cycles of math) would leave the pipe waiting.
 // ============================================================================
-#ifndef B200_PF_KST
-#define B200_PF_KST 3
-#endif
-#ifndef B200_PF_VST
-#define B200_PF_VST 3
-#endif
-constexpr int kTcKStages = B200_PF_KST;   // 32 KB per stage
-constexpr int kTcVStages = B200_PF_VST;
-#ifndef B200_PF_KLEAD
-#define B200_PF_KLEAD 2
-#endif
-constexpr int kTcKLead = B200_PF_KLEAD;   // K loads run this many tiles ahead of the V loads
+// Ring depths and the K lead were chosen by A/B timing on the part (2 + 4 and 4 + 2 stages and
+// leads of 0 and 1 were each 0.5-2 % slower).
+constexpr int kTcKStages = 3;             // 32 KB per stage
+constexpr int kTcVStages = 3;
+constexpr int kTcKLead = 2;               // K loads run this many tiles ahead of the V loads
 constexpr int kTcSoftmaxThreads = 256;
 constexpr int kTcEpilogueThreads = 128;
 constexpr int kTcThreads = kTcSoftmaxThreads + 128 + kTcEpilogueThreads;   // whole warpgroups: 512 = 4 x 128
