@@ -63,6 +63,25 @@ def test_group_sizes(n_q, n_kv):
     torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
 
 
+def test_many_ragged_items_per_cta():
+    """Forty-eight sequences of random query and prefix lengths: more work items than
+    CTAs, items of one to eight KV tiles, ragged last row tiles - every CTA goes through
+    several item hand-overs (mailbox, accumulator release, row-sum exchange)."""
+    from auto_infer_b200 import synth
+    g = torch.Generator().manual_seed(77)
+    q_lens = torch.randint(5, 301, (48,), generator=g).tolist()
+    prefixes = torch.randint(0, 701, (48,), generator=g).tolist()
+    seqs = [(q, q + p) for q, p in zip(q_lens, prefixes)]
+    blocks = sum((kv + 127) // 128 for _, kv in seqs) + 4
+    b = synth.build_gqa_batch("ragged", seqs, 8, 2, 128, blocks, 78)
+    ref, ref_lse = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table,
+                                       b.cu_seqlens_q, b.seqlens_kv, b.scale, return_lse=True)
+    out, lse = _prefill(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                        b.seqlens_kv, b.scale, b.n_q, b.n_kv, want_lse=True)
+    torch.testing.assert_close(out.float(), ref.float(), **TOL)
+    torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
+
+
 def test_context_parallel_slice_with_rows_that_see_no_key():
     """The keys [128, 200) of a 200-token prompt as one context-parallel rank holds them
     (local block table, local length, causal base in local coordinates): the first 128
