@@ -3,7 +3,6 @@
 // per CTA, so every SM streams the same number of bytes whatever the context
 // length distribution (the per-step host lists it consumes are the ones
 // auto_infer/worker/model_runner.py:126-136 builds).
-#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -112,11 +111,7 @@ static int build_split_plan(const char* who, int tile_tokens, const int32_t* cu_
       if (q_len > 0 && kv_lens[b] > 0 && q_len * group <= kMaxRows) pairs += num_kv_heads;
     }
   }
-  static const int overhead_tiles = [] {
-    const char* e = getenv("B200_ITEM_OVERHEAD_TILES");   // tuning knob, default kItemOverheadTiles
-    return e ? atoi(e) : kItemOverheadTiles;
-  }();
-  const int64_t item_cost = total >= 8 * (int64_t)num_ctas ? overhead_tiles : 0;   // tiny steps: pure tile balance
+  const int64_t item_cost = total >= 8 * (int64_t)num_ctas ? kItemOverheadTiles : 0;   // tiny steps: pure tile balance
   const int64_t total_cost = total + item_cost * (pairs + num_ctas);
   const int64_t quota_lo = total_cost / num_ctas;
   const int rem = (int)(total_cost % num_ctas);

@@ -823,5 +823,4 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   return check_cuda(launch_pdl(paged_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), smem_tc,
                                static_cast<cudaStream_t>(stream), k_map, v_map, q_map, p),
                     "paged_prefill_gqa launch");
-  return check_cuda(cudaGetLastError(), "paged_prefill_gqa launch");
 }

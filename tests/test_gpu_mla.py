@@ -5,9 +5,9 @@ import pytest
 import torch
 
 from oracle import paged_attention_oracle as orc
+from tests.parity import TOL, assert_attention_close, assert_scale_free
 
 pytestmark = pytest.mark.gpu
-TOL = dict(atol=2e-2, rtol=2e-2)
 
 
 def _mla(q_latent, cache, bt, cu, kv, scale, heads, num_ctas=None, want_lse=False):
@@ -29,7 +29,7 @@ def test_golden_latent_rows_from_the_reference_core(golden_small):
         bt = torch.arange(nb, dtype=torch.int32)[None]
         for num_ctas in (None, 1, 3):
             got = _mla(q, cache, bt, [1], [kv_len], lat["scale"], 16, num_ctas=num_ctas)
-            torch.testing.assert_close(got.float(), o.float(), **TOL)
+            assert_attention_close(got, o, what=f"golden latent row kv_len={kv_len} ctas={num_ctas}")
 
 
 @pytest.mark.parametrize("ctx,bs", [(1, 128), (31, 128), (32, 128), (33, 128), (128, 128), (129, 128),
@@ -42,18 +42,17 @@ def test_page_and_tile_boundaries(ctx, bs):
                                        b.seqlens_kv, b.scale, return_lse=True)
     out, lse = _mla(b.q, b.kv_cache, b.block_table, b.cu_seqlens_q, b.seqlens_kv, b.scale, 16,
                     want_lse=True)
-    torch.testing.assert_close(out.float(), ref[..., :512].float(), **TOL)
-    torch.testing.assert_close(lse, ref_lse, atol=2e-3, rtol=2e-3)
+    assert_attention_close(out, ref[..., :512], lse, ref_lse)
 
 
 def test_fewer_heads_and_two_query_rows():
     """8 heads x 2 query rows fill the 16 MMA rows (multi-token verify shape)."""
     from auto_infer_b200 import synth
     b = synth.build_mla_batch("mtp", [(2, 300), (1, 77), (2, 2)], 8, 16, 91)
-    ref = orc.paged_attention(b.q, b.kv_cache, b.kv_cache, b.block_table, b.cu_seqlens_q,
-                              b.seqlens_kv, b.scale)
-    out = _mla(b.q, b.kv_cache, b.block_table, b.cu_seqlens_q, b.seqlens_kv, b.scale, 8)
-    torch.testing.assert_close(out.float(), ref[..., :512].float(), **TOL)
+    ref, ref_lse = orc.paged_attention(b.q, b.kv_cache, b.kv_cache, b.block_table, b.cu_seqlens_q,
+                                       b.seqlens_kv, b.scale, return_lse=True)
+    out, lse = _mla(b.q, b.kv_cache, b.block_table, b.cu_seqlens_q, b.seqlens_kv, b.scale, 8, want_lse=True)
+    assert_attention_close(out, ref[..., :512], lse, ref_lse)
 
 
 @pytest.mark.parametrize("batch", [4, 16, 64])
@@ -67,15 +66,21 @@ def test_config3_full_size_with_absorbed_projections(batch):
     orc.write_kv(b.k_new, None, b.kv_cache, None, b.slot_mapping.tolist())
     assert torch.equal(d.kv_cache.cpu(), b.kv_cache)
     plan = ops.MlaDecodePlan(b.cu_seqlens_q, b.seqlens_kv, 16, "cuda")
-    o_latent = ops.mla_decode_absorbed(d.q, d.kv_cache, d.block_table, plan, b.scale)
+    lse = torch.empty(b.num_tokens, 16, dtype=torch.float32, device="cuda")
+    o_latent = ops.mla_decode_absorbed(d.q, d.kv_cache, d.block_table, plan, b.scale, lse_out=lse)
+    o_latent32 = ops.mla_decode_absorbed(d.q, d.kv_cache, d.block_table, plan, b.scale, out_f32=True)
     out = torch.einsum("tnl,nvl->tnv", o_latent, d.extra["w_uv"]).cpu()
     ref = orc.mla_absorbed_attention(b.extra["q_nope"], b.extra["q_pe"], b.kv_cache, b.block_table,
                                      b.cu_seqlens_q, b.seqlens_kv, b.scale, b.extra["w_uk"],
                                      b.extra["w_uv"])
+    # the final rows pass through one more bf16 contraction (W_UV) on each side: the stated
+    # tolerance plus a row-relative L2 bound; the kernel's own output is held to the full check
     torch.testing.assert_close(out.float(), ref.float(), **TOL)
-    ref_latent = orc.mla_latent_attention(b.q, b.kv_cache, b.block_table, b.cu_seqlens_q,
-                                          b.seqlens_kv, b.scale, 512)
-    torch.testing.assert_close(o_latent.cpu().float(), ref_latent.float(), **TOL)
+    assert_scale_free(out, ref, "rows after W_UV", atol_rms=5e-2, rtol=2e-2, rel_l2=2e-2)
+    full, ref_lse = orc.paged_attention(b.q, b.kv_cache, b.kv_cache, b.block_table, b.cu_seqlens_q,
+                                        b.seqlens_kv, b.scale, return_lse=True)
+    assert_attention_close(o_latent.cpu(), full[..., :512], lse.cpu(), ref_lse, "latent rows (bf16)")
+    assert_attention_close(o_latent32.cpu(), full[..., :512], what="latent rows (fp32)")
     assert ops.read_status("cuda") == 0
 
 

@@ -118,3 +118,64 @@ def test_backends_refuse_to_run_without_cuda_tensors():
     k = torch.zeros(1, 2, 128, dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         backend.paged_attention(0, q, k, k, ctx)
+
+
+# --------------------------------------------------------------------------- #
+# the documented integration step, against the reference's own registry
+# --------------------------------------------------------------------------- #
+def _reference_registry():
+    """auto-infer's registry module, or skip: the reference tree is only present on
+    the build machine (``PYTHONPATH`` or the sibling checkout)."""
+    import importlib
+    import os
+    import sys
+    try:
+        return importlib.import_module("auto_infer.layers.attention.registry")
+    except ImportError:
+        pass
+    sibling = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                           "reference")
+    if os.path.isdir(os.path.join(sibling, "auto_infer")):
+        sys.path.insert(0, sibling)
+        try:
+            return importlib.import_module("auto_infer.layers.attention.registry")
+        except ImportError:
+            sys.path.remove(sibling)
+    pytest.skip("auto_infer (the reference runtime) is not importable here")
+
+
+def test_install_into_auto_infer_serves_the_reference_builders():
+    """After ``install_into_auto_infer()`` the REFERENCE's ``build_attention_backend`` /
+    ``build_mtp_attention_backend`` (auto_infer/layers/attention/registry.py:119-157) build
+    the B200 backends for models that opt in by family name, and hand mode 'dense' to the
+    reference's own eager backends."""
+    ref = _reference_registry()
+    if "gqa_b200" not in ref._FAMILIES:
+        names = registry.install_into_auto_infer()
+        assert set(names) == {"gqa_b200", "mla_b200"}
+    with pytest.raises(ValueError, match="already registered"):
+        registry.install_into_auto_infer()
+
+    backend, caches = ref.build_attention_backend(_gqa_model("gqa_b200"), "paged", num_blocks=3, block_size=128)
+    assert isinstance(backend, B200GqaBackend)
+    assert len(caches) == 3 and caches[0].shape == (2, 3, 128, 2, 128)
+    backend, caches = ref.build_attention_backend(_gqa_model("gqa_b200"), "graph", num_blocks=3, block_size=128)
+    assert isinstance(backend, B200GqaBackend)
+
+    from auto_infer.layers.attention.gqa import DenseBackend
+    from auto_infer.layers.attention.mla import MlaDenseBackend
+    dense, caches = ref.build_attention_backend(_gqa_model("gqa_b200"), "dense")
+    assert isinstance(dense, DenseBackend) and caches == []
+    mla_model = _mla_model()
+    mla_model.ATTENTION_FAMILY = "mla_b200"
+    dense, _ = ref.build_attention_backend(mla_model, "dense")
+    assert isinstance(dense, MlaDenseBackend)
+    backend, caches = ref.build_attention_backend(mla_model, "paged", num_blocks=2, block_size=128)
+    assert isinstance(backend, B200MlaBackend) and caches[0][0].shape == (2, 128, 1, 576)
+
+    mtp, caches = ref.build_mtp_attention_backend(_gqa_model("gqa_b200"), "paged", "model.mtp_layers.0.",
+                                                  num_blocks=2, block_size=128)
+    assert isinstance(mtp, B200GqaBackend) and mtp.num_layers == 1
+    assert mtp.layer_prefix(0) == "model.mtp_layers.0." and len(caches) == 1
+    with pytest.raises(ValueError, match="unsupported MTP attention mode"):
+        ref.build_mtp_attention_backend(_gqa_model("gqa_b200"), "dense", "model.mtp_layers.0.")
