@@ -14,13 +14,14 @@ B200_OK = 0
 STATUS_BAD_SLOT = 1
 STATUS_BAD_BLOCK = 2
 STATUS_WAIT_TIMEOUT = 4
+STATUS_BAD_LAUNCH = 8
 
 
 class DecodePlanInfo(ctypes.Structure):
     """Mirror of ``b200_decode_plan_info``."""
     _fields_ = [(name, c_int32) for name in (
         "num_ctas", "num_items", "num_partials", "num_multi",
-        "total_tiles", "skipped_seqs", "plan_ints", "reserved")]
+        "total_tiles", "skipped_seqs", "plan_ints", "mode")]
 
 
 class PrefillPlanInfo(ctypes.Structure):
@@ -44,6 +45,10 @@ SIGNATURES = {
     "b200_paged_decode_gqa": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, POINTER(DecodePlanInfo), c_int, c_int, c_int, c_float,
+        c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_paged_decode_gqa_replayable": (c_int, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+        c_void_p, c_int, c_int, c_int, c_int, c_float,
         c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_paged_decode_gqa_static": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,

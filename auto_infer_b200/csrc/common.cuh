@@ -131,6 +131,12 @@ __device__ __forceinline__ void mbar_wait_bounded(uint64_t* bar, uint32_t parity
   mbar_wait_slow(bar, parity, cta_abort, status, limit_ns);
 }
 
+// Orders this thread's earlier generic-proxy accesses to shared memory before later
+// accesses by the async proxy (TMA) to the same bytes.
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

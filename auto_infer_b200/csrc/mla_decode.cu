@@ -105,10 +105,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   const int lane = threadIdx.x & 31;
 
   const int32_t* plan = p.plan;
-  const int32_t* cta_off = plan + plan[kHdrOffCta];
+  const CtaRecord* cta_rec = reinterpret_cast<const CtaRecord*>(plan + plan[kHdrOffCta]) + blockIdx.x;
   const DecodeItem* items = reinterpret_cast<const DecodeItem*>(plan + plan[kHdrOffItems]);
-  const int item_begin = cta_off[blockIdx.x];
-  const int item_end = cta_off[blockIdx.x + 1];
+  const int item_begin = cta_rec->item_begin;
+  const int item_end = cta_rec->item_end;
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;

@@ -14,15 +14,15 @@
 //   * at the end of an item the eight warps merge their (m, l, O) through shared
 //     memory in a fixed order (deterministic) and write either the final bf16
 //     rows (the item covered the whole pair) or one fp32 partial (o, lse).
-// A second small kernel (split_merge.cuh, launched with programmatic dependent
-// launch) merges the partials of pairs that were cut; merging inside this kernel
-// by the last-arriving CTA was tried and put the merge's dependent L2 loads on the
-// consumers' critical path for no gain.
+// The partial records of a pair that was cut are merged by the CTA whose record
+// arrives last (one arrival counter per cut pair in the plan).  That CTA only notes
+// the pair and carries on with its own items; the merges it owes run once, after its
+// last item, so the dependent L2 loads of a merge never sit between two items and a
+// layer-step needs no second kernel.
 //
 // Algorithmic bytes per launch: sum_b kv_len_b * 2 * Hkv * 128 * 2 B (+ q, o).
 #include "common.cuh"
 #include "decode_plan.h"
-#include "split_merge.cuh"
 
 namespace b200 {
 
@@ -41,6 +41,7 @@ constexpr int kHalfTileBytes = kTileTokens * 128;            // [64 tokens][64 d
 constexpr int kTileBytes = 2 * kHalfTileBytes;               // K or V tile of one stage
 constexpr int kStageBytes = 2 * kTileBytes;                  // K + V
 constexpr int kSlotFloats = kMaxRows * kHeadDim;             // one warp's O in the merge buffer
+constexpr int kRecFloats = kMaxRows * kHeadDim + kMaxRows;   // partial record: o (16 x 128), then lse (16)
 
 struct __align__(1024) DecodeSmem {
   uint8_t stage[kStages][kStageBytes];                       // [K lo | K hi | V lo | V hi]
@@ -50,6 +51,8 @@ struct __align__(1024) DecodeSmem {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   int abort_flag;
+  int merge_count;                                           // cut pairs whose last record this CTA wrote
+  int merge_list[kMaxDeferred];
 };
 
 static_assert(sizeof(DecodeSmem) + 1024 <= 227 * 1024, "shared memory budget of one CTA");
@@ -59,9 +62,8 @@ struct DecodeParams {
   int64_t q_stride;                 // elements between query tokens
   const int32_t* block_table;
   int64_t bt_stride;
-  int32_t* plan;                    // the pairs' arrival counters in it are updated by the kernel
-  float* part_o;                    // (num_partials, 16, 128) fp32
-  float* part_lse;                  // (num_partials, 16)
+  int32_t* plan;                    // the arrival counters of its cut pairs are counted up and put back to zero
+  float* part;                      // partial records, kRecFloats each
   void* out;                        // (T, Hq, 128) bf16 or fp32
   float* lse_out;                   // (T, Hq) or null
   int32_t* status;
@@ -72,7 +74,7 @@ struct DecodeParams {
   int block_size, block_shift, num_blocks;
   int box_tokens, boxes_per_tile;
   int out_is_f32;
-  int off_cta, off_items, off_multi;   // plan offsets (derivable from the grid size and item count)
+  int max_partials;                 // records the workspace holds
   float scale, scale_log2;
 };
 
@@ -81,18 +83,72 @@ struct TileWalker {
   const DecodeItem* items;
   int item, item_end, tile, tile_end;
   DecodeItem cur;
+  __device__ __forceinline__ void set(const int4& a, const int4& b, const int4& c) {
+    cur.seq = a.x; cur.kv_head = a.y; cur.tile_begin = a.z; cur.tile_end = a.w;
+    cur.kv_len = b.x; cur.q_start = b.y; cur.q_len = b.z; cur.causal_base = b.w;
+    cur.partial_idx = c.x; cur.direct = c.y; cur.multi_idx = c.z;
+    tile = cur.tile_begin;
+    tile_end = cur.tile_end;
+  }
   __device__ __forceinline__ void load() {
     if (item < item_end) {
       const int4* p = reinterpret_cast<const int4*>(items + item);
-      int4 a = __ldg(p), b = __ldg(p + 1), c = __ldg(p + 2);
-      cur.seq = a.x; cur.kv_head = a.y; cur.tile_begin = a.z; cur.tile_end = a.w;
-      cur.kv_len = b.x; cur.q_start = b.y; cur.q_len = b.z; cur.causal_base = b.w;
-      cur.partial_idx = c.x; cur.direct = c.y; cur.multi_idx = c.z;
-      tile = cur.tile_begin;
-      tile_end = cur.tile_end;
+      set(__ldg(p), __ldg(p + 1), __ldg(p + 2));
     }
   }
 };
+
+// Merge of the partial records of the cut pairs a CTA has noted, by its 256 consumer
+// threads: thread -> (row, 8 columns) of the pair's 16 x 128 result.  Records are read
+// with L2 loads (other CTAs wrote them) in record order, so the sum does not depend on
+// which CTA happens to run the merge.
+__device__ __forceinline__ void merge_noted_pairs(const DecodeParams& p, const int* list, int count,
+                                               int off_multi) {
+  const int t = threadIdx.x;
+  const int row = t >> 4;
+  const int col = (t & 15) * 8;
+  const int G = p.group;
+  for (int e = 0; e < count; ++e) {
+    const MultiGroup* mg = reinterpret_cast<const MultiGroup*>(p.plan + off_multi) + list[e];
+    const int pb = __ldcg(&mg->part_begin), pe = __ldcg(&mg->part_end);
+    const int q_start = __ldcg(&mg->q_start), q_len = __ldcg(&mg->q_len), kv_head = __ldcg(&mg->kv_head);
+    if (row >= q_len * G) continue;
+    const float* rec = p.part + (int64_t)pb * kRecFloats;
+    const int n = pe - pb;
+    float mx = -INFINITY;
+#pragma unroll 4
+    for (int i = 0; i < n; ++i) mx = fmaxf(mx, __ldcg(rec + (int64_t)i * kRecFloats + kMaxRows * kHeadDim + row));
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float wsum = 0.f;
+#pragma unroll 4
+    for (int i = 0; i < n; ++i) {
+      const float* r = rec + (int64_t)i * kRecFloats;
+      const float l = __ldcg(r + kMaxRows * kHeadDim + row);
+      const float wgt = (l == -INFINITY) ? 0.f : __expf(l - mx);
+      const float4* src = reinterpret_cast<const float4*>(r + row * kHeadDim + col);
+      const float4 a = __ldcg(src), b = __ldcg(src + 1);
+      wsum += wgt;
+      acc[0] += wgt * a.x; acc[1] += wgt * a.y; acc[2] += wgt * a.z; acc[3] += wgt * a.w;
+      acc[4] += wgt * b.x; acc[5] += wgt * b.y; acc[6] += wgt * b.z; acc[7] += wgt * b.w;
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    const int64_t tok = q_start + row / G;
+    const int head = kv_head * G + row % G;
+    const int64_t off = (tok * p.num_q_heads + head) * kHeadDim + col;
+    if (p.out_is_f32) {
+      float* dst = reinterpret_cast<float*>(p.out) + off;
+      *reinterpret_cast<float4*>(dst) = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+      *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+    } else {
+      uint4 pk;
+      pk.x = pack_bf16(acc[0] * inv, acc[1] * inv); pk.y = pack_bf16(acc[2] * inv, acc[3] * inv);
+      pk.z = pack_bf16(acc[4] * inv, acc[5] * inv); pk.w = pack_bf16(acc[6] * inv, acc[7] * inv);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pk;
+    }
+    if (p.lse_out && (t & 15) == 0)
+      p.lse_out[tok * p.num_q_heads + head] = wsum > 0.f ? mx + __logf(wsum) : -INFINITY;
+  }
+}
 
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
@@ -104,14 +160,20 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // The plan is host-built and reaches the device by a copy, never by the kernel in
+  // front of this one: its words may be read before the grid dependency is resolved.
   const int32_t* plan = p.plan;
-  const int32_t* cta_off = plan + p.off_cta;
-  const DecodeItem* items = reinterpret_cast<const DecodeItem*>(plan + p.off_items);
-  const int item_begin = cta_off[blockIdx.x];
-  const int item_end = cta_off[blockIdx.x + 1];
+  const int4* rec = reinterpret_cast<const int4*>(plan + kPlanHeaderInts + kCtaInts * blockIdx.x);
+  const int4 r0 = __ldg(rec), r1 = __ldg(rec + 1), r2 = __ldg(rec + 2), r3 = __ldg(rec + 3);
+  const int4 hdr0 = __ldg(reinterpret_cast<const int4*>(plan));
+  const int4 hdr1 = __ldg(reinterpret_cast<const int4*>(plan) + 1);
+  const int item_begin = r0.x;
+  const int item_end = r0.y;
+  const DecodeItem* items = reinterpret_cast<const DecodeItem*>(plan + hdr1.z);   // kHdrOffItems
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    sm.merge_count = 0;
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 4);     // one arrival per warp of the consuming group
@@ -120,13 +182,20 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   }
   __syncthreads();
 #ifdef B200_TRACE
-  if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 0] = (long long)global_timer_ns();
+  if (p.trace && threadIdx.x == 0) {
+    p.trace[blockIdx.x * 16 + 0] = (long long)global_timer_ns();
+    p.trace[blockIdx.x * 16 + 15] = clock64();
+  }
 #endif
   grid_dep_launch();              // the next kernel may be scheduled; it waits for this grid itself
-  grid_dep_wait();                // q and the step's new cache rows come from earlier kernels
+  grid_dep_wait();                // q, the block table and the step's new cache rows come from earlier kernels
 #ifdef B200_TRACE
   if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 1] = (long long)global_timer_ns();
 #endif
+  if (hdr0.x != kPlanMagic || hdr0.y != (int)gridDim.x) {      // not a plan for this launch
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200_STATUS_BAD_LAUNCH);
+    return;
+  }
   if (item_begin >= item_end) return;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -137,28 +206,48 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       tma_prefetch_desc(&v_map);
     }
     TileWalker w{items, item_begin, item_end, 0, 0, {}};
-    w.load();
+    w.set(r1, r2, r3);
     uint32_t it = 0;
     const int nbox = p.boxes_per_tile;
-    // block id of this lane's box for the current tile (lane < nbox)
-    auto fetch_block = [&](const TileWalker& tw) -> int {
-      if (lane >= nbox) return 0;
-      const int last_block = (tw.cur.kv_len - 1) >> p.block_shift;
-      int lb = ((tw.tile * kTileTokens) >> p.block_shift) + lane;
-      lb = lb > last_block ? last_block : lb;       // tail boxes re-read the last valid page
-      return __ldg(p.block_table + (int64_t)tw.cur.seq * p.bt_stride + lb);
-    };
-    int bid = fetch_block(w);
-    while (w.item < w.item_end) {
-      // look one tile ahead so the block-table read overlaps the wait below
-      TileWalker nxt = w;
-      ++nxt.tile;
-      if (nxt.tile >= nxt.tile_end) {
-        ++nxt.item;
-        nxt.load();
+    // Block ids come out of a register window: lane l holds the id of logical block
+    // win_base + l of the current sequence (32 blocks = 64 tiles at block_size 128), and the
+    // window after it is already on its way.  A tile's boxes never straddle a window (the box
+    // count divides 32), so one shuffle per tile replaces a dependent trip to L2 per tile,
+    // which would hold a CTA that streams alone to one tile per round trip.
+    int win_seq = -1, win_base = 0, win_ids = 0, nxt_ids = 0;
+    // the item after the current one is fetched when the current one starts
+    int4 na = r1, nb = r2, nc = r3;
+    auto prefetch_item = [&](int idx) {
+      if (idx < item_end) {
+        const int4* ip = reinterpret_cast<const int4*>(items + idx);
+        na = __ldg(ip); nb = __ldg(ip + 1); nc = __ldg(ip + 2);
       }
-      int bid_next = 0;
-      if (nxt.item < nxt.item_end) bid_next = fetch_block(nxt);
+    };
+    prefetch_item(item_begin + 1);
+    auto load_window = [&](int seq, int base, int kv_len) -> int {
+      const int last_block = (kv_len - 1) >> p.block_shift;
+      int lb = base + lane;
+      lb = lb > last_block ? last_block : lb;         // past the end: any valid entry of the row
+      return __ldg(p.block_table + (int64_t)seq * p.bt_stride + lb);
+    };
+    while (w.item < w.item_end) {
+      const int first_lb = (w.tile * kTileTokens) >> p.block_shift;
+      const int base = first_lb & ~31;
+      if (w.cur.seq != win_seq || base != win_base) {
+        if (w.cur.seq == win_seq && base == win_base + 32) {
+          win_ids = nxt_ids;                          // the prefetched window
+        } else {
+          win_ids = load_window(w.cur.seq, base, w.cur.kv_len);
+        }
+        win_seq = w.cur.seq;
+        win_base = base;
+        nxt_ids = load_window(w.cur.seq, base + 32, w.cur.kv_len);   // used 32 blocks from now, if at all
+      }
+      // this lane's box of the tile (lanes >= nbox idle); tail boxes re-read the last valid page
+      const int last_block = (w.cur.kv_len - 1) >> p.block_shift;
+      int lb = first_lb + (lane < nbox ? lane : 0);
+      lb = lb > last_block ? last_block : lb;
+      const int bid = __shfl_sync(0xffffffffu, win_ids, lb - win_base);
 
       const int s = it % kStages;
       const uint32_t ph = (it / kStages) & 1u;
@@ -186,8 +275,14 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       }
       __syncwarp();
       ++it;
-      w = nxt;
-      bid = bid_next;
+      ++w.tile;
+      if (w.tile >= w.tile_end) {
+        ++w.item;
+        if (w.item < w.item_end) {
+          w.set(na, nb, nc);
+          prefetch_item(w.item + 1);
+        }
+      }
     }
     // drain: do not leave while copies may still land in this CTA's shared memory
     if (lane == 0) {
@@ -214,7 +309,7 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   const int v_chunk_sel = lane >> 4;                                 // V: matrices 2,3 -> dims +8
 
   TileWalker w{items, item_begin, item_end, 0, 0, {}};
-  w.load();
+  w.set(r1, r2, r3);
   uint32_t it = 0;
 
   // Q fragments of an item: 8 k-steps x 4 registers, rows beyond q_len*group are zero.
@@ -240,6 +335,38 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     }
   };
   load_q(w.cur);
+
+  // A partial record is announced (arrival counter of its pair) one item late, or at the end
+  // of the CTA's work: by then its stores have long left the SM and the fence that must
+  // precede the announcement costs nothing, where a fence right behind the stores would
+  // hold all eight warps for a round trip through a loaded memory system.
+  int pending_multi = -1;
+  const int off_multi = hdr1.w;
+  auto announce = [&](int multi_idx) {            // thread 0, after a fence by all and a barrier
+    MultiGroup* mg = reinterpret_cast<MultiGroup*>(p.plan + off_multi) + multi_idx;
+    const int n_parts = mg->part_end - mg->part_begin;
+    if (atomicAdd(&mg->arrivals, 1) == n_parts - 1) {
+      mg->arrivals = 0;                           // ready for the next launch on this plan
+      __threadfence();                            // the other CTAs' records are visible from here on
+      if (sm.merge_count < kMaxDeferred) {
+        sm.merge_list[sm.merge_count] = multi_idx;
+        sm.merge_count = sm.merge_count + 1;
+      } else if (p.status) {                      // the planner never gives a CTA this many cut pieces
+        atomicOr(p.status, B200_STATUS_BAD_LAUNCH);
+      }
+    }
+  };
+  // the record of the item after the current one, fetched while the current one streams
+  // (its first two quarters: what the Q fetch needs; the rest is read at the hand-over and
+  // not used before the item ends)
+  int4 na = r1, nb = r2;
+  auto prefetch_item = [&](int idx) {
+    if (idx < item_end) {
+      const int4* ip = reinterpret_cast<const int4*>(items + idx);
+      na = __ldg(ip); nb = __ldg(ip + 1);
+    }
+  };
+  prefetch_item(item_begin + 1);
 
   while (w.item < w.item_end) {
     const DecodeItem item = w.cur;
@@ -320,6 +447,20 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
         pf[2] = pack_bf16(pr[1][0], pr[1][1]);
         pf[3] = pack_bf16(pr[1][2], pr[1][3]);
       }
+      // ---- rows past the sequence's end carry weight 0, but 0 x NaN is NaN: whatever bytes
+      // an unwritten cache slot holds must not reach the MMA.  Only a pair's last tile has
+      // such rows; the warp clears its own 16 of them in shared memory.
+      const bool ragged = (tile + 1) * kTileTokens > item.kv_len;
+      if (ragged) {
+        const int first_bad = item.kv_len - tile * kTileTokens;          // first row of the tile past the end
+        for (int idx = lane; idx < 16 * 16; idx += 32) {
+          const int row = wslice * 16 + (idx >> 4), chunk = idx & 15;
+          if (row >= first_bad)
+            *reinterpret_cast<uint4*>(sm.stage[s] + kTileBytes + (chunk >> 3) * kHalfTileBytes +
+                                      swz128(row, chunk & 7)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        __syncwarp();
+      }
       // ---- O += P V (k = this warp's 16 tokens, n = 128 dims)
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -329,6 +470,7 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
         mma_bf16_16816(o[2 * j], pf, vb[0], vb[1]);
         mma_bf16_16816(o[2 * j + 1], pf, vb[2], vb[3]);
       }
+      if (ragged) fence_proxy_async();      // the stage goes back to TMA: order these stores before its writes
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.empty[s]);
 #ifdef B200_TRACE
@@ -340,10 +482,17 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
 #endif
     }
 
+#ifdef B200_TRACE_PHASES
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 14] = (long long)global_timer_ns();
+#endif
     // ---- next item's Q on its way, then merge the eight warps (fixed order) and write the result
     ++w.item;
-    w.load();
-    if (w.item < w.item_end) load_q(w.cur);
+    if (w.item < w.item_end) {
+      w.set(na, nb, __ldg(reinterpret_cast<const int4*>(items + w.item) + 2));
+      prefetch_item(w.item + 1);
+      load_q(w.cur);
+    }
+    if (pending_multi >= 0) __threadfence();      // stores of the PREVIOUS partial record (long done)
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
@@ -354,7 +503,14 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       sm.red_l[warp][quad] = l0;
       sm.red_l[warp][quad + 8] = l1;
     }
-    named_bar_sync(1, kConsumerThreads);
+    named_bar_sync(1, kConsumerThreads);                       // (1) every warp's m and l are in place
+#ifdef B200_TRACE_PHASES
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 10] = (long long)global_timer_ns();
+#endif
+    if (pending_multi >= 0) {
+      if (threadIdx.x == 0) announce(pending_multi);
+      pending_multi = -1;
+    }
     {
       float g0 = -INFINITY, g1 = -INFINITY;
 #pragma unroll
@@ -369,86 +525,128 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
         o[n][0] *= f0; o[n][1] *= f0; o[n][2] *= f1; o[n][3] *= f1;
       }
     }
+    // Merge-buffer rows are 128 floats, a multiple of the 32 banks: the eight fragment rows a
+    // warp stores at once would all land in the same banks.  Column groups of 8 floats are
+    // XOR-ed with the row number (mod 4), which spreads them over all banks.
+    const int swz = (quad & 3) << 3;              // same for row quad and row quad + 8
     auto store_slot = [&](float* slot) {
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
-        const int col = n * 8 + qlane * 2;
+        const int col = (n * 8 + qlane * 2) ^ swz;
         *reinterpret_cast<float2*>(slot + quad * kHeadDim + col) = make_float2(o[n][0], o[n][1]);
         *reinterpret_cast<float2*>(slot + (quad + 8) * kHeadDim + col) = make_float2(o[n][2], o[n][3]);
       }
     };
     if (warp >= 4) store_slot(sm.slots[warp - 4]);
-    named_bar_sync(1, kConsumerThreads);
+    named_bar_sync(1, kConsumerThreads);                       // (2)
+#ifdef B200_TRACE_PHASES
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 11] = (long long)global_timer_ns();
+#endif
     if (warp < 4) {
       const float* slot = sm.slots[warp];
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
-        const int col = n * 8 + qlane * 2;
+        const int col = (n * 8 + qlane * 2) ^ swz;
         const float2 a = *reinterpret_cast<const float2*>(slot + quad * kHeadDim + col);
         const float2 b = *reinterpret_cast<const float2*>(slot + (quad + 8) * kHeadDim + col);
         o[n][0] += a.x; o[n][1] += a.y; o[n][2] += b.x; o[n][3] += b.y;
       }
     }
-    named_bar_sync(1, kConsumerThreads);
+    named_bar_sync(1, kConsumerThreads);                       // (3)
+#ifdef B200_TRACE_PHASES
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 12] = (long long)global_timer_ns();
+#endif
     if (warp < 4) store_slot(sm.slots[warp]);
-    named_bar_sync(1, kConsumerThreads);
-    {
-      // 256 threads: thread -> (row, 8 columns)
-      const int t = threadIdx.x;
-      const int row = t >> 4;
-      const int col = (t & 15) * 8;
+    // 256 threads: thread -> rows (t / 32) and (t / 32 + 8), 4 columns each, so a warp reads and
+    // writes whole rows.  The rows' maxima and sums are taken from red_m / red_l BEFORE
+    // barrier (4): no warp writes those arrays again (next item) until every thread has
+    // passed (4), i.e. has finished reading them.
+    const int t = threadIdx.x;
+    const int col = (t & 31) * 4;
+    float inv_r[2], lse_r[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = (t >> 5) + h * 8;
+      float g = -INFINITY, lsum = 0.f;
       if (row < rows) {
-        float g = -INFINITY;
 #pragma unroll
         for (int ww = 0; ww < kConsumerWarps; ++ww) g = fmaxf(g, sm.red_m[ww][row]);
-        float lsum = 0.f;
 #pragma unroll
         for (int ww = 0; ww < kConsumerWarps; ++ww) {
           const float mw = sm.red_m[ww][row];
           lsum += (mw == -INFINITY) ? 0.f : sm.red_l[ww][row] * fast_exp2((mw - g) * p.scale_log2);
         }
-        const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-        float v[8];
+      }
+      inv_r[h] = lsum > 0.f ? 1.f / lsum : 0.f;
+      lse_r[h] = lsum > 0.f ? g * p.scale + __logf(lsum) : -INFINITY;
+    }
+    named_bar_sync(1, kConsumerThreads);                       // (4) the four slots hold the warp-pair sums
+#ifdef B200_TRACE_PHASES
+    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 13] = (long long)global_timer_ns();
+#endif
+    const bool record_fits = item.direct || item.partial_idx < p.max_partials;
 #pragma unroll
-        for (int c = 0; c < 8; c += 4) {
-          float4 acc = *reinterpret_cast<const float4*>(&sm.slots[0][row * kHeadDim + col + c]);
+    for (int h = 0; h < 2; ++h) {
+      const int row = (t >> 5) + h * 8;
+      if (row >= rows || !record_fits) continue;
+      const int pcol = col ^ ((row & 3) << 3);
+      float4 acc = *reinterpret_cast<const float4*>(&sm.slots[0][row * kHeadDim + pcol]);
 #pragma unroll
-          for (int sl = 1; sl < 4; ++sl) {
-            const float4 x = *reinterpret_cast<const float4*>(&sm.slots[sl][row * kHeadDim + col + c]);
-            acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
-          }
-          v[c] = acc.x * inv; v[c + 1] = acc.y * inv; v[c + 2] = acc.z * inv; v[c + 3] = acc.w * inv;
-        }
-        const float lse = lsum > 0.f ? g * p.scale + __logf(lsum) : -INFINITY;
-        if (item.direct) {
-          const int64_t tok = item.q_start + row / G;
-          const int head = item.kv_head * G + row % G;
-          const int64_t off = (tok * p.num_q_heads + head) * kHeadDim + col;
-          if (p.out_is_f32) {
-            float* dst = reinterpret_cast<float*>(p.out) + off;
-            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-          } else {
-            uint4 pk;
-            pk.x = pack_bf16(v[0], v[1]); pk.y = pack_bf16(v[2], v[3]);
-            pk.z = pack_bf16(v[4], v[5]); pk.w = pack_bf16(v[6], v[7]);
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pk;
-          }
-          if (p.lse_out && (t & 15) == 0) p.lse_out[tok * p.num_q_heads + head] = lse;
+      for (int sl = 1; sl < 4; ++sl) {
+        const float4 x = *reinterpret_cast<const float4*>(&sm.slots[sl][row * kHeadDim + pcol]);
+        acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      }
+      const float inv = inv_r[h];
+      const float4 v = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+      if (item.direct) {
+        const int64_t tok = item.q_start + row / G;
+        const int head = item.kv_head * G + row % G;
+        const int64_t off = (tok * p.num_q_heads + head) * kHeadDim + col;
+        if (p.out_is_f32) {
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off) = v;
         } else {
-          float* dst = p.part_o + ((int64_t)item.partial_idx * kMaxRows + row) * kHeadDim + col;
-          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-          *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-          if ((t & 15) == 0) p.part_lse[(int64_t)item.partial_idx * kMaxRows + row] = lse;
+          uint2 pk;
+          pk.x = pack_bf16(v.x, v.y);
+          pk.y = pack_bf16(v.z, v.w);
+          *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pk;
         }
+        if (p.lse_out && (t & 31) == 0) p.lse_out[tok * p.num_q_heads + head] = lse_r[h];
+      } else {
+        float* rec = p.part + (int64_t)item.partial_idx * kRecFloats;
+        *reinterpret_cast<float4*>(rec + row * kHeadDim + col) = v;
+        if ((t & 31) == 0) rec[kMaxRows * kHeadDim + row] = lse_r[h];
+      }
+    }
+    if (!item.direct) {
+      if (record_fits) {
+        pending_multi = item.multi_idx;
+      } else if (t == 0 && p.status) {
+        atomicOr(p.status, B200_STATUS_BAD_LAUNCH);            // workspace smaller than the plan needs
       }
     }
 #ifdef B200_TRACE
     if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 5] = (long long)global_timer_ns();   // item written
 #endif
-    // the next item's first shared-memory write of the merge area comes after
-    // its own first barrier, which no thread passes before finishing the reads above
+    // The next item's first write to red_m / red_l comes after barrier (4) above, and its first
+    // write to the slots after its own barrier (1), which no thread passes before it has
+    // finished the reads of this item.
   }
+
+  // ---- the last record's announcement, then the merges this CTA owes: the cut pairs
+  // whose last record it wrote
+  if (pending_multi >= 0) {
+    __threadfence();
+    named_bar_sync(1, kConsumerThreads);
+    if (threadIdx.x == 0) announce(pending_multi);
+  }
+  named_bar_sync(1, kConsumerThreads);
+  if (sm.merge_count > 0) merge_noted_pairs(p, sm.merge_list, sm.merge_count, off_multi);
+#ifdef B200_TRACE
+  if (p.trace && threadIdx.x == 0) {
+    p.trace[blockIdx.x * 16 + 9] = (long long)global_timer_ns();   // merges done
+    p.trace[blockIdx.x * 16 + 15] = clock64() - p.trace[blockIdx.x * 16 + 15];
+  }
+#endif
 }
 
 }  // namespace b200
@@ -458,44 +656,46 @@ static long long* g_trace = nullptr;
 extern "C" void b200_debug_set_trace(void* dev_ptr) { g_trace = static_cast<long long*>(dev_ptr); }
 #endif
 
-extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void* key_cache,
-                                     const void* value_cache, int num_blocks, int block_size,
-                                     const int32_t* block_table, int64_t bt_stride,
-                                     int32_t* plan_dev, const b200_decode_plan_info* info,
-                                     int num_q_heads, int num_kv_heads, int head_dim, float scale,
-                                     void* workspace, size_t workspace_bytes, void* out,
-                                     int out_is_f32, float* lse_out, int32_t* status,
-                                     void* stream) {
-  using namespace b200;
-  if (!info) {
-    set_last_error("paged_decode_gqa: plan info is null");
-    return B200_EINVAL;
-  }
-  if (info->num_items == 0) return B200_OK;
+namespace b200 {
+
+// Shared launcher.  With `info` the counts of the step are known on the host (nothing
+// is launched for an empty plan, the workspace only has to hold the records the plan
+// uses).  Without it every count is read from the plan on the device: the launch then
+// depends on num_ctas alone and can be recorded once and replayed for other steps.
+static int launch_decode(const char* who, const void* q, int64_t q_stride, const void* key_cache,
+                         const void* value_cache, int num_blocks, int block_size,
+                         const int32_t* block_table, int64_t bt_stride, int32_t* plan_dev,
+                         const b200_decode_plan_info* info, int num_ctas, int num_q_heads,
+                         int num_kv_heads, int head_dim, float scale, void* workspace,
+                         size_t workspace_bytes, void* out, int out_is_f32, float* lse_out,
+                         int32_t* status, void* stream) {
   if (!q || !key_cache || !value_cache || !block_table || !plan_dev || !out || !workspace ||
-      num_blocks <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads) {
-    set_last_error("paged_decode_gqa: null pointer or bad head counts");
+      num_blocks <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads ||
+      num_ctas <= 0) {
+    set_last_error("%s: null pointer, bad head counts or no CTAs", who);
     return B200_EINVAL;
   }
   if (head_dim != kHeadDim) {
-    set_last_error("paged_decode_gqa: head_dim %d unsupported (kernel is built for 128)", head_dim);
+    set_last_error("%s: head_dim %d unsupported (kernel is built for 128)", who, head_dim);
     return B200_EUNSUPPORTED;
   }
   if (block_size < 8 || (block_size & (block_size - 1))) {
-    set_last_error("paged_decode_gqa: block_size %d must be a power of two >= 8", block_size);
+    set_last_error("%s: block_size %d must be a power of two >= 8", who, block_size);
     return B200_EUNSUPPORTED;
   }
   if (reinterpret_cast<uintptr_t>(q) % 4 || (q_stride % 2) || q_stride < (int64_t)num_q_heads * head_dim) {
-    set_last_error("paged_decode_gqa: q must be 4-byte aligned with an even token stride >= Hq*D");
+    set_last_error("%s: q must be 4-byte aligned with an even token stride >= Hq*D", who);
     return B200_EALIGN;
   }
-  if (reinterpret_cast<uintptr_t>(out) % 16 || reinterpret_cast<uintptr_t>(workspace) % 16) {
-    set_last_error("paged_decode_gqa: out and workspace must be 16-byte aligned");
+  if (reinterpret_cast<uintptr_t>(out) % 16 || reinterpret_cast<uintptr_t>(workspace) % 16 ||
+      reinterpret_cast<uintptr_t>(plan_dev) % 16) {
+    set_last_error("%s: out, workspace and plan must be 16-byte aligned", who);
     return B200_EALIGN;
   }
-  const size_t need = (size_t)info->num_partials * (kMaxRows * (size_t)kHeadDim + kMaxRows) * sizeof(float);
-  if (workspace_bytes < need) {
-    set_last_error("paged_decode_gqa: workspace %zu bytes < %zu needed", workspace_bytes, need);
+  const size_t max_partials = workspace_bytes / (kRecFloats * sizeof(float));
+  if (info && (size_t)info->num_partials > max_partials) {
+    set_last_error("%s: workspace %zu bytes < %zu needed", who, workspace_bytes,
+                   (size_t)info->num_partials * kRecFloats * sizeof(float));
     return B200_EPLAN;
   }
   const int box_tokens = block_size < kTileTokens ? block_size : kTileTokens;
@@ -511,11 +711,8 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
   p.block_table = block_table;
   p.bt_stride = bt_stride;
   p.plan = plan_dev;
-  p.off_cta = kPlanHeaderInts;
-  p.off_items = p.off_cta + round_up4(info->num_ctas + 1);
-  p.off_multi = p.off_items + kItemInts * info->num_items;
-  p.part_o = static_cast<float*>(workspace);
-  p.part_lse = p.part_o + (size_t)info->num_partials * kMaxRows * kHeadDim;
+  p.part = static_cast<float*>(workspace);
+  p.max_partials = max_partials > (size_t)INT32_MAX ? INT32_MAX : (int)max_partials;
   p.out = out;
   p.lse_out = lse_out;
   p.status = status;
@@ -546,17 +743,46 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
     if (rc) return rc;
     if (dev < 64) attr_set[dev] = true;
   }
-  rc = check_cuda(launch_pdl(paged_decode_gqa_kernel, dim3(info->num_ctas), dim3(kDecodeThreads), smem, s,
-                             k_map, v_map, p),
-                  "paged_decode_gqa launch");
-  if (rc) return rc;
-  if (info->num_multi > 0) {
-    rc = check_cuda(launch_pdl(split_merge_kernel<kHeadDim>, dim3(split_merge_grid<kHeadDim>(info->num_multi)),
-                               dim3(128), 0, s, (const int32_t*)plan_dev, (const float*)p.part_o,
-                               (const float*)p.part_lse, out, lse_out, num_q_heads, p.group, out_is_f32),
-                    "decode_merge launch");
+  return check_cuda(launch_pdl(paged_decode_gqa_kernel, dim3(num_ctas), dim3(kDecodeThreads), smem, s,
+                               k_map, v_map, p),
+                    "paged_decode_gqa launch");
+}
+
+}  // namespace b200
+
+extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void* key_cache,
+                                     const void* value_cache, int num_blocks, int block_size,
+                                     const int32_t* block_table, int64_t bt_stride,
+                                     int32_t* plan_dev, const b200_decode_plan_info* info,
+                                     int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                     void* workspace, size_t workspace_bytes, void* out,
+                                     int out_is_f32, float* lse_out, int32_t* status,
+                                     void* stream) {
+  using namespace b200;
+  if (!info) {
+    set_last_error("paged_decode_gqa: plan info is null");
+    return B200_EINVAL;
   }
-  return rc;
+  if (info->num_items == 0) return B200_OK;
+  return launch_decode("paged_decode_gqa", q, q_stride, key_cache, value_cache, num_blocks, block_size,
+                       block_table, bt_stride, plan_dev, info, info->num_ctas, num_q_heads, num_kv_heads,
+                       head_dim, scale, workspace, workspace_bytes, out, out_is_f32, lse_out, status,
+                       stream);
+}
+
+extern "C" int b200_paged_decode_gqa_replayable(const void* q, int64_t q_stride, const void* key_cache,
+                                                const void* value_cache, int num_blocks, int block_size,
+                                                const int32_t* block_table, int64_t bt_stride,
+                                                int32_t* plan_dev, int num_ctas, int num_q_heads,
+                                                int num_kv_heads, int head_dim, float scale,
+                                                void* workspace, size_t workspace_bytes, void* out,
+                                                int out_is_f32, float* lse_out, int32_t* status,
+                                                void* stream) {
+  using namespace b200;
+  return launch_decode("paged_decode_gqa_replayable", q, q_stride, key_cache, value_cache, num_blocks,
+                       block_size, block_table, bt_stride, plan_dev, nullptr, num_ctas, num_q_heads,
+                       num_kv_heads, head_dim, scale, workspace, workspace_bytes, out, out_is_f32,
+                       lse_out, status, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -571,7 +797,7 @@ extern "C" int b200_paged_decode_gqa(const void* q, int64_t q_stride, const void
 // ---------------------------------------------------------------------------
 namespace b200 {
 constexpr int kStaticMaxPartials = 1024;   // (o, lse) records; 8 256 B each -> 8.06 MiB in total
-constexpr size_t kStaticScratchFloats = (size_t)kStaticMaxPartials * (kMaxRows * kHeadDim + kMaxRows);
+constexpr size_t kStaticScratchFloats = (size_t)kStaticMaxPartials * kRecFloats;
 static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
 }  // namespace b200
 

@@ -119,36 +119,67 @@ class DecodePlan:
     """Host plan + device copy + workspace for one step of split-KV decode.
     Built once per step from the two host length lists and shared by all layers
     (the reference hands the same lists to its vendor op per layer,
-    auto_infer/layers/attention/gqa.py:91-92)."""
+    auto_infer/layers/attention/gqa.py:91-92).
+
+    With ``capacity_seqs`` the plan is *replayable*: its device buffer and workspace
+    are sized for any step of at most that many sequences and keep their
+    addresses, ``refill()`` overwrites the plan in place, and the attention launch
+    depends on ``num_ctas`` only, so a CUDA graph that recorded it serves later
+    steps (what the reference's per-layer task update does on the host,
+    auto_infer/layers/attention/graph_fia.py:70-104)."""
 
     def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_q_heads: int,
                  num_kv_heads: int, device, head_dim: int = 128, num_ctas: Optional[int] = None,
-                 causal_base: Optional[Sequence[int]] = None):
+                 causal_base: Optional[Sequence[int]] = None, capacity_seqs: Optional[int] = None):
         lib = _lib.load()
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("DecodePlan needs a CUDA device (no CPU fallback)")
-        self.num_seqs = len(cu_seqlens_q)
         self.num_q_heads, self.num_kv_heads, self.head_dim = num_q_heads, num_kv_heads, head_dim
         self.num_ctas = int(num_ctas) if num_ctas else sm_count(self.device)
-        nbytes = lib.b200_decode_plan_bytes(self.num_seqs, num_kv_heads, self.num_ctas)
-        self.host = torch.empty(nbytes // 4, dtype=torch.int32, pin_memory=True)
+        self.replayable = capacity_seqs is not None
+        self.capacity_seqs = max(int(capacity_seqs), len(cu_seqlens_q)) if self.replayable else len(cu_seqlens_q)
+        self._nbytes = lib.b200_decode_plan_bytes(self.capacity_seqs, num_kv_heads, self.num_ctas)
+        self.host = torch.empty(self._nbytes // 4, dtype=torch.int32, pin_memory=True)
+        self.info = DecodePlanInfo()
+        self._build(cu_seqlens_q, seqlens_kv, causal_base)
+        used = max(int(self.info.plan_ints), 16)
+        if self.replayable:
+            self.dev = torch.zeros(self._nbytes // 4, dtype=torch.int32, device=self.device)
+            ws = lib.b200_decode_workspace_bytes(self.capacity_seqs, num_kv_heads, self.num_ctas, head_dim)
+        else:
+            self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
+            ws = (self.info.num_partials * (16 * head_dim + 16)) * 4 + 256
+        self.dev[:used].copy_(self.host[:used], non_blocking=True)
+        self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
+
+    def _build(self, cu_seqlens_q, seqlens_kv, causal_base) -> None:
+        lib = _lib.load()
+        self.num_seqs = len(cu_seqlens_q)
+        if self.num_seqs > self.capacity_seqs:
+            raise ValueError(f"{self.num_seqs} sequences exceed the plan's capacity of {self.capacity_seqs}")
         cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
         kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
         base_ptr = None
         if causal_base is not None:
             base = torch.tensor(list(causal_base), dtype=torch.int32)
             base_ptr = base.data_ptr()
-        self.info = DecodePlanInfo()
         rc = lib.b200_decode_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, self.num_seqs,
-                                  num_q_heads, num_kv_heads, self.num_ctas,
-                                  self.host.data_ptr(), nbytes, ctypes.byref(self.info))
+                                  self.num_q_heads, self.num_kv_heads, self.num_ctas,
+                                  self.host.data_ptr(), self._nbytes, ctypes.byref(self.info))
         _lib.check(rc, "b200_decode_plan")
+
+    def refill(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int],
+               causal_base: Optional[Sequence[int]] = None) -> None:
+        """Plan another step into the same buffers: host planning, then one pinned ->
+        device copy on the current stream (ahead of the replay that reads it)."""
+        if not self.replayable:
+            raise RuntimeError("refill() needs a plan built with capacity_seqs")
+        # the previous copy out of the pinned buffer must have left before it is overwritten
+        torch.cuda.current_stream(self.device).synchronize()
+        self._build(cu_seqlens_q, seqlens_kv, causal_base)
         used = max(int(self.info.plan_ints), 16)
-        self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
-        self.dev.copy_(self.host[:used], non_blocking=True)
-        ws = (self.info.num_partials * (16 * head_dim + 16)) * 4 + 256
-        self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
+        self.dev[:used].copy_(self.host[:used], non_blocking=True)
 
     @property
     def skipped_seqs(self) -> int:
@@ -179,14 +210,24 @@ def paged_decode_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torc
     elif not out.is_contiguous():
         raise ValueError("out must be contiguous")
     with _on_device(q.device):
-        rc = lib.b200_paged_decode_gqa(
-            q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
-            num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
-            plan.dev.data_ptr(), ctypes.byref(plan.info), n_q, n_kv, d, float(scale),
-            plan.workspace.data_ptr(), plan.workspace.numel(), out.data_ptr(),
-            1 if out.dtype == torch.float32 else 0,
-            lse_out.data_ptr() if lse_out is not None else None,
-            status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        if plan.replayable:
+            rc = lib.b200_paged_decode_gqa_replayable(
+                q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
+                num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+                plan.dev.data_ptr(), plan.num_ctas, n_q, n_kv, d, float(scale),
+                plan.workspace.data_ptr(), plan.workspace.numel(), out.data_ptr(),
+                1 if out.dtype == torch.float32 else 0,
+                lse_out.data_ptr() if lse_out is not None else None,
+                status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        else:
+            rc = lib.b200_paged_decode_gqa(
+                q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
+                num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+                plan.dev.data_ptr(), ctypes.byref(plan.info), n_q, n_kv, d, float(scale),
+                plan.workspace.data_ptr(), plan.workspace.numel(), out.data_ptr(),
+                1 if out.dtype == torch.float32 else 0,
+                lse_out.data_ptr() if lse_out is not None else None,
+                status_word(q.device).data_ptr(), _stream_ptr(q.device))
     _lib.check(rc, "b200_paged_decode_gqa")
     return out
 

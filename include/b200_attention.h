@@ -76,9 +76,12 @@ int b200_reshape_and_cache(const void* key, const void* value,
  * lists per step (cumulative query lengths, per-sequence kv lengths:
  * auto_infer/worker/model_runner.py:126-136, forward_context.py:15-16).  Here
  * the same two lists are turned, once per step and for all layers, into a flat
- * work list: the 64-token KV tiles of every (sequence, kv head) pair are laid
- * end to end and cut into num_ctas equal ranges, so every CTA streams the same
- * number of bytes whatever the length distribution.
+ * work list of 64-token KV tile runs of the (sequence, kv head) pairs, dealt to
+ * num_ctas persistent CTAs: whole pairs (or a few equal pieces of a long pair)
+ * packed longest first when the step is small or the packing comes out
+ * balanced, otherwise all tiles laid end to end and cut into num_ctas ranges of
+ * equal cost, so that every CTA streams the same number of bytes whatever the
+ * length distribution.
  *
  * Sequences whose q_len * (Hq/Hkv) exceeds 16 rows are left out (they belong to
  * b200_paged_prefill_gqa); their count is reported in info->skipped_seqs.
@@ -86,16 +89,20 @@ int b200_reshape_and_cache(const void* key, const void* value,
  * causal_base may be NULL (then kv_len - q_len is used): key j of sequence b is
  * visible to its query row i iff j <= causal_base[b] + i.  A context-parallel
  * rank passes its local kv lengths and a base shifted by its slice offset.
+ *
+ * Every offset inside the plan depends on (num_seqs, num_kv_heads, num_ctas)
+ * only, so a buffer of b200_decode_plan_bytes() can be refilled step after step
+ * at one device address (see b200_paged_decode_gqa_replayable).
  */
 typedef struct b200_decode_plan_info {
   int32_t num_ctas;        /* grid of the decode kernel                         */
-  int32_t num_items;       /* work items (CTA range x (seq, kv head))           */
+  int32_t num_items;       /* work items (tile runs)                            */
   int32_t num_partials;    /* partial (o, lse) records the kernel writes        */
-  int32_t num_multi;       /* (seq, kv head) groups merged by the combine pass  */
-  int32_t total_tiles;     /* 64-token tiles over all groups                    */
+  int32_t num_multi;       /* (seq, kv head) pairs cut into several items       */
+  int32_t total_tiles;     /* KV tiles over all pairs                           */
   int32_t skipped_seqs;    /* sequences too wide for the decode kernel          */
   int32_t plan_ints;       /* int32 words of the plan actually used             */
-  int32_t reserved;
+  int32_t mode;            /* 1: whole pieces packed, 0: streaming cut          */
 } b200_decode_plan_info;
 
 /* Upper bounds for sizing buffers before the lengths are known. */
@@ -115,14 +122,21 @@ int b200_decode_plan(const int32_t* cu_seqlens_q_host, const int32_t* seqlens_kv
  *   q (T, Hq, 128) bf16, row stride q_stride elements
  *   caches (num_blocks, block_size, Hkv, 128) bf16; block_size a power of two >= 8
  *   block_table (B, >= blocks needed) int32, row stride bt_stride
- *   plan_dev: device copy of the plan built by b200_decode_plan; not const: it holds one
- *             arrival counter per cut pair that the kernel counts up and puts back to zero,
- *             so one plan serves all layers of a step as long as calls sharing it do not
- *             overlap on the GPU
- *   workspace: b200_decode_workspace_bytes() bytes, 256-byte aligned
+ *   plan_dev: device copy of the plan built by b200_decode_plan (info->plan_ints words),
+ *             16-byte aligned; it must reach the device by a copy, not be written by the
+ *             kernel launched just before this call.  Not const: it holds one arrival
+ *             counter per cut pair, which the kernel counts up and puts back to zero (the
+ *             CTA that completes a pair's records merges them, so there is no second
+ *             kernel); one plan serves all layers of a step as long as calls sharing it
+ *             do not overlap on the GPU
+ *   workspace: room for info->num_partials records of 16*128+16 floats
+ *             (b200_decode_workspace_bytes() is the upper bound for any plan of that
+ *             geometry), 16-byte aligned
  *   out: (T, Hq, 128) bf16 when out_is_f32 == 0, fp32 otherwise (the fp32 form
  *        is one context-parallel rank's partial); lse_out (T, Hq) fp32 or NULL
- * Mask: bottom-right causal (sparse_mode 3 of the vendor op). */
+ * Mask: bottom-right causal (sparse_mode 3 of the vendor op).  Cache rows past a
+ * sequence's kv_len (the unwritten tail of its last page) are never read into the
+ * arithmetic: they may hold any bytes. */
 int b200_paged_decode_gqa(const void* q, int64_t q_stride,
                           const void* key_cache, const void* value_cache,
                           int num_blocks, int block_size,
@@ -132,6 +146,33 @@ int b200_paged_decode_gqa(const void* q, int64_t q_stride,
                           void* workspace, size_t workspace_bytes,
                           void* out, int out_is_f32, float* lse_out,
                           int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * The same attention as a launch that can be recorded once and replayed for
+ * other steps (CUDA graph).  Replaces what the reference's graph mode does on
+ * the host for every layer of every replay: re-issuing the attention task with
+ * the step's length lists (GraphFiaLifecycle.update / update_many,
+ * auto_infer/layers/attention/graph_fia.py:70-104).  Here the lengths live in
+ * the plan on the device; nothing about the launch depends on them:
+ *   - the grid is num_ctas, the counts and offsets are read from plan_dev by the
+ *     kernel, nothing is skipped for an empty plan;
+ *   - plan_dev has b200_decode_plan_bytes(num_seqs, Hkv, num_ctas) bytes and the
+ *     workspace b200_decode_workspace_bytes(num_seqs, Hkv, num_ctas, 128) bytes,
+ *     so that any later plan built for at most num_seqs sequences with the same
+ *     num_ctas fits; before each replay the caller copies the new plan (its
+ *     info->plan_ints words) to the same address, on the same stream or as a
+ *     copy node of the graph from a fixed pinned buffer.
+ * A plan built for another num_ctas sets B200_STATUS_BAD_LAUNCH and nothing is
+ * computed. */
+int b200_paged_decode_gqa_replayable(const void* q, int64_t q_stride,
+                                     const void* key_cache, const void* value_cache,
+                                     int num_blocks, int block_size,
+                                     const int32_t* block_table, int64_t bt_stride,
+                                     int32_t* plan_dev, int num_ctas,
+                                     int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                     void* workspace, size_t workspace_bytes,
+                                     void* out, int out_is_f32, float* lse_out,
+                                     int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * Paged GQA attention for wide query blocks: chunked prefill over a cached
@@ -195,6 +236,9 @@ int b200_paged_prefill_gqa(const void* q, int64_t q_stride,
  *     in full before it is read.  Two calls whose kernels overlap on the GPU
  *     (different streams) race on it; keep such calls on one stream or order
  *     them with events.
+ *   - The looked-up address is kept per device in a table that is filled without
+ *     a lock: two threads making the first call at once both look the same
+ *     address up and store the same value.
  * All other arguments, outputs and return codes are those of
  * b200_paged_decode_gqa. */
 int b200_paged_decode_gqa_static(const void* q, int64_t q_stride,

@@ -33,35 +33,113 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
     assert b"sm_100a" in lib.b200_version()
 
 
-def test_plan_is_pure_host_code(lib):
+def _plan(lib, cu, kv, n_q, n_kv, num_ctas, mla=False):
+    """(info, header, per-CTA item lists, items, multi groups) of a host-built plan."""
     import torch
     from auto_infer_b200._lib import DecodePlanInfo
-    cu = torch.tensor([1, 2, 4], dtype=torch.int32)
-    kv = torch.tensor([100, 65, 130], dtype=torch.int32)
-    nbytes = lib.b200_decode_plan_bytes(3, 2, 4)
+    cu_t = torch.tensor(cu, dtype=torch.int32)
+    kv_t = torch.tensor(kv, dtype=torch.int32)
+    heads = 1 if mla else n_kv
+    nbytes = lib.b200_decode_plan_bytes(len(cu), heads, num_ctas)
     buf = torch.zeros(nbytes // 4, dtype=torch.int32)
     info = DecodePlanInfo()
-    rc = lib.b200_decode_plan(cu.data_ptr(), kv.data_ptr(), None, 3, 8, 2, 4, buf.data_ptr(), nbytes,
-                              ctypes.byref(info))
-    assert rc == 0
-    tiles = (2 + 2 + 3) * 2
-    assert info.total_tiles == tiles and info.num_ctas == 4
+    if mla:
+        rc = lib.b200_mla_decode_plan(cu_t.data_ptr(), kv_t.data_ptr(), None, len(cu), n_q, num_ctas,
+                                      buf.data_ptr(), nbytes, ctypes.byref(info))
+    else:
+        rc = lib.b200_decode_plan(cu_t.data_ptr(), kv_t.data_ptr(), None, len(cu), n_q, n_kv, num_ctas,
+                                  buf.data_ptr(), nbytes, ctypes.byref(info))
+    assert rc == 0, lib.b200_last_error()
     hdr = buf[:16].tolist()
-    cta_off = buf[hdr[5]:hdr[5] + 5].tolist()
+    assert hdr[1] == num_ctas and hdr[2] == info.num_items and hdr[10] == info.mode
+    assert info.plan_ints == hdr[6] + 12 * info.num_items and info.plan_ints * 4 <= nbytes
+    recs = buf[hdr[5]:hdr[5] + 16 * num_ctas].view(-1, 16).tolist()
     items = buf[hdr[6]:hdr[6] + 12 * info.num_items].view(-1, 12).tolist()
-    per_cta = [sum(it[3] - it[2] for it in items[cta_off[c]:cta_off[c + 1]]) for c in range(4)]
-    assert sum(per_cta) == tiles and max(per_cta) - min(per_cta) <= 1
-    # every (seq, head) pair is covered exactly once, in order
+    multi = buf[hdr[7]:hdr[7] + 8 * info.num_multi].view(-1, 8).tolist()
+    assert hdr[7] + 8 * info.num_multi <= hdr[6]             # the groups end before the items start
+    per_cta = []
+    for rec in recs:
+        mine = items[rec[0]:rec[1]]
+        if mine:
+            assert rec[4:16] == mine[0]                      # the record carries a copy of the first item
+        per_cta.append(mine)
+    return info, hdr, per_cta, items, multi
+
+
+def _check_cover(items, multi, kv, n_kv, tile, info):
+    """Every (seq, head) pair is covered exactly once; the records of a cut pair are numbered
+    consecutively in tile order and listed in its group."""
     cover = {}
     for it in items:
-        cover.setdefault((it[0], it[1]), []).append((it[2], it[3]))
+        cover.setdefault((it[0], it[1]), []).append((it[2], it[3], it[8], it[9], it[10]))
+    assert len(cover) == sum(1 for k in kv if k > 0) * n_kv
+    parts = 0
     for (seq, _), runs in cover.items():
+        runs.sort()
         assert runs[0][0] == 0 and all(a[1] == b[0] for a, b in zip(runs, runs[1:]))
-        assert runs[-1][1] == (kv[seq].item() + 63) // 64
-    # partial records are numbered consecutively per pair and listed for the merge
-    multi = buf[hdr[7]:hdr[7] + 8 * info.num_multi].view(-1, 8).tolist()
-    assert sum(m[4] - m[3] for m in multi) == info.num_partials
-    assert all((it[9] == 1) == (it[8] == -1) for it in items)
+        assert runs[-1][1] == (kv[seq] + tile - 1) // tile
+        if len(runs) == 1:
+            assert runs[0][2] == -1 and runs[0][3] == 1
+        else:
+            group = multi[runs[0][4]]
+            assert [r[2] for r in runs] == list(range(group[3], group[4]))
+            assert all(r[3] == 0 and r[4] == runs[0][4] for r in runs)
+            parts += len(runs)
+    assert parts == info.num_partials == sum(m[4] - m[3] for m in multi)
+
+
+def test_plan_is_pure_host_code(lib):
+    cu, kv = [1, 2, 4], [100, 65, 130]
+    info, hdr, per_cta, items, multi = _plan(lib, cu, kv, 8, 2, 4)
+    tiles = (2 + 2 + 3) * 2
+    assert info.total_tiles == tiles and info.num_ctas == 4
+    assert sum(it[3] - it[2] for it in items) == tiles
+    _check_cover(items, multi, kv, 2, 64, info)
+
+
+def test_plan_modes_on_the_benchmark_shapes(lib):
+    """Small steps and many-pair steps keep pairs whole (no partial records at all where the
+    pairs fit); the 128K-context step is cut into equal streams."""
+    from auto_infer_b200 import synth
+    import torch
+    g = torch.Generator().manual_seed(synth.SEED_BASE + 1)
+    c1 = synth._uniform_lengths(g, 16, 512, 2048)
+    info, _, per_cta, items, multi = _plan(lib, list(range(1, 17)), c1, 16, 8, 148)
+    assert info.mode == 1 and info.num_partials == 0 and info.num_items == 128
+    _check_cover(items, multi, c1, 8, 64, info)
+    assert max(len(m) for m in per_cta) <= 3
+
+    g = torch.Generator().manual_seed(synth.SEED_BASE + 2)
+    c2 = synth._uniform_lengths(g, 60, 256, 8192)
+    info, _, per_cta, items, multi = _plan(lib, list(range(1, 61)), c2, 32, 8, 148)
+    assert info.mode == 1 and info.num_partials == 0 and info.num_items == 480
+    loads = [sum(it[3] - it[2] for it in mine) for mine in per_cta]
+    assert max(loads) <= 1.10 * sum(loads) / 148
+    _check_cover(items, multi, c2, 8, 64, info)
+
+    # config 5 on one GPU: long streams, cut to equal cost
+    kv = [131072] * 8
+    info, _, per_cta, items, multi = _plan(lib, list(range(1, 9)), kv, 64, 8, 148)
+    assert info.mode == 0
+    loads = [sum(it[3] - it[2] for it in mine) for mine in per_cta]
+    assert max(loads) - min(loads) <= 20 and max(len(m) for m in per_cta) <= 3
+    assert sum(1 for mine in per_cta for it in mine if it[9] == 0) == info.num_partials
+    assert max(sum(1 for it in mine if it[9] == 0) for mine in per_cta) <= 2
+    _check_cover(items, multi, kv, 8, 64, info)
+    # one of eight context-parallel ranks: every pair in two halves, one piece per CTA
+    kv = [131072 // 8] * 8
+    info, _, per_cta, items, multi = _plan(lib, list(range(1, 9)), kv, 64, 8, 148)
+    assert info.mode == 1 and info.num_items == 128 and info.num_multi == 64
+    assert max(len(m) for m in per_cta) == 1
+    _check_cover(items, multi, kv, 8, 64, info)
+
+    # the latent kernel is not bandwidth-shared: uneven packing is never taken for it
+    g = torch.Generator().manual_seed(synth.SEED_BASE + 3)
+    c3 = synth._uniform_lengths(g, 64, 1024, 8192)
+    info, _, per_cta, items, multi = _plan(lib, list(range(1, 65)), c3, 16, 1, 148, mla=True)
+    loads = [sum(it[3] - it[2] for it in mine) for mine in per_cta]
+    assert max(loads) <= 1.12 * sum(loads) / 148 + 8
+    _check_cover(items, multi, c3, 1, 32, info)
 
 
 def test_plan_rejects_bad_arguments(lib):

@@ -76,8 +76,8 @@ def test_static_scratch_entry_matches_workspace_entry_twice_in_a_row():
 def test_static_scratch_entry_refuses_oversized_plans():
     from auto_infer_b200 import _lib, ops, synth
     lib = _lib.load()
-    b = synth.build_gqa_batch("noalloc_big", [(1, 16384)] * 2, 16, 8, 128, 256, 43).to("cuda")
-    plan = ops.DecodePlan(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, "cuda", num_ctas=1500)
+    b = synth.build_gqa_batch("noalloc_big", [(1, 65536)] * 2, 16, 8, 128, 1024, 43, device="cuda")
+    plan = ops.DecodePlan(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, "cuda", num_ctas=3000)
     assert plan.info.num_partials > 1024
     out = torch.zeros(b.q.shape, dtype=torch.bfloat16, device="cuda")
     rc = _call_static(lib, b, plan, out)
