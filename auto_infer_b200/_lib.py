@@ -72,7 +72,7 @@ SIGNATURES = {
         c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_cp_exchange_buffer_bytes": (c_size_t, [c_int, c_int64, c_int]),
     "b200_cp_exchange_combine": (c_int, [
-        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int,
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int64,
         c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_lse_combine": (c_int, [
         c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int,

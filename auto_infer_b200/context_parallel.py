@@ -76,7 +76,9 @@ class PartialBuffer:
         self.lse = self.flat[self.rows * head_dim:].view(num_tokens, num_q_heads)
 
     def clear(self) -> None:
-        """Rows a rank has no keys for must read as an empty part."""
+        """Every row reads as an empty part (the decode plan writes every row of its
+        sequences itself, also those a rank has no keys for; this is for buffers filled
+        by hand)."""
         self.o.zero_()
         self.lse.fill_(float("-inf"))
 
@@ -123,12 +125,15 @@ class PeerExchange:
 
 
 class ContextParallelDecode:
-    """Holds the per-step plan and buffers of one CP rank and runs a layer-step."""
+    """Holds the plan and buffers of one CP rank and runs layer-steps.  Buffers and
+    the plan's device address are fixed for the object's life: ``replan()`` refills
+    them for the next step's lengths, so a step costs host planning and one small
+    copy, and a CUDA graph recorded by ``capture()`` stays valid."""
 
     def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv_global: Sequence[int],
                  num_q_heads: int, num_kv_heads: int, head_dim: int, block_size: int, device,
                  group=None, cp_rank: Optional[int] = None, cp_size: Optional[int] = None,
-                 exchange: Optional["PeerExchange"] = None):
+                 exchange: Optional["PeerExchange"] = None, capacity_seqs: Optional[int] = None):
         self.group = group
         self.exchange = exchange          # None: NCCL all-gather + merge kernel
         if cp_size is None:
@@ -136,17 +141,29 @@ class ContextParallelDecode:
         if cp_rank is None:
             cp_rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.cp_rank, self.cp_size = cp_rank, cp_size
+        self.block_size = block_size
         self.local_kv, self.offsets, self.bases = shard_lengths(
             seqlens_kv_global, cu_seqlens_q, block_size, cp_rank, cp_size)
         self.meta = StepMetadata(cu_seqlens_q, self.local_kv, num_q_heads, num_kv_heads, head_dim,
-                                 device, causal_base=self.bases)
+                                 device, causal_base=self.bases,
+                                 capacity_seqs=capacity_seqs or len(cu_seqlens_q))
         if self.meta.prefill_seqs:
             raise NotImplementedError("context-parallel attention is built for decode-shaped rows")
         self.num_tokens = self.meta.num_tokens
         self.partial = PartialBuffer(self.num_tokens, num_q_heads, head_dim, device)
-        self.has_empty = any(k == 0 for k in self.local_kv)
         self.out = torch.empty(self.num_tokens, num_q_heads, head_dim, dtype=torch.bfloat16,
                                device=device)
+
+    def replan(self, cu_seqlens_q: Sequence[int], seqlens_kv_global: Sequence[int]) -> None:
+        """Lengths of the next step (same number of query tokens): the local plan is
+        refilled in place."""
+        if (cu_seqlens_q[-1] if len(cu_seqlens_q) else 0) != self.num_tokens:
+            raise ValueError("replan() keeps the step's token count; build a new object for another shape")
+        self.local_kv, self.offsets, self.bases = shard_lengths(
+            seqlens_kv_global, cu_seqlens_q, self.block_size, self.cp_rank, self.cp_size)
+        self.meta.rebuild(cu_seqlens_q, self.local_kv, causal_base=self.bases)
+        if self.meta.prefill_seqs:
+            raise NotImplementedError("context-parallel attention is built for decode-shaped rows")
 
     def capture(self, q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                 local_block_table: torch.Tensor, scale: float, before=None):
@@ -182,8 +199,6 @@ class ContextParallelDecode:
         if self.cp_size == 1:
             return ops.paged_decode_gqa(q, key_cache, value_cache, local_block_table,
                                         self.meta.decode, scale, out=self.out)
-        if self.has_empty:
-            self.partial.clear()
         ops.paged_decode_gqa(q, key_cache, value_cache, local_block_table, self.meta.decode, scale,
                              out=self.partial.o, lse_out=self.partial.lse)
         if self.exchange is not None:

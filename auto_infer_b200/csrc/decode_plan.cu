@@ -124,7 +124,7 @@ bool pack_whole_pieces(const std::vector<Pair>& pairs, int64_t total, int num_ct
   pieces.reserve(pairs.size() + num_ctas);
   for (size_t i = 0; i < pairs.size(); ++i) {
     const int t = pairs[i].tiles;
-    const int k = (int)((t + cap - 1) / cap);
+    const int k = t > 0 ? (int)((t + cap - 1) / cap) : 1;
     const int lo = t / k, rem = t % k;
     int at = 0;
     for (int j = 0; j < k; ++j) {
@@ -202,11 +202,15 @@ static int build_split_plan(const char* who, int tile_tokens, bool bandwidth_sha
       set_last_error("%s: sequence %d has negative length", who, b);
       return B200_EINVAL;
     }
-    if (q_len == 0 || kv_lens[b] == 0) continue;
+    if (q_len == 0) continue;
     if (q_len * group > kMaxRows) {
-      ++skipped;
+      if (kv_lens[b] > 0) ++skipped;
       continue;
     }
+    // A sequence without keys (the empty slice of a context-parallel rank) still gets an
+    // item per kv head, with no tile: its rows come out as zeros with lse = -inf, so the
+    // output of a step is fully written whatever the lengths.  (GQA kernel only.)
+    if (kv_lens[b] == 0 && !bandwidth_shared) continue;
     const int tiles = (kv_lens[b] + tile_tokens - 1) / tile_tokens;
     const int base = causal_base ? causal_base[b] : kv_lens[b] - q_len;
     for (int h = 0; h < num_kv_heads; ++h)
@@ -231,14 +235,14 @@ static int build_split_plan(const char* who, int tile_tokens, bool bandwidth_sha
   int n_items = 0;
   int mode = 0;
   std::vector<std::vector<Piece>> per_cta;
-  if (total > 0 && pack_whole_pieces(pairs, total, num_ctas, max_items, bandwidth_shared, &per_cta)) {
+  if (!pairs.empty() && pack_whole_pieces(pairs, total, num_ctas, max_items, bandwidth_shared, &per_cta)) {
     mode = 1;
     for (int c = 0; c < num_ctas; ++c) {
       ctas[c].item_begin = n_items;
       for (const Piece& pc : per_cta[c]) items[n_items++] = make_item(pairs[pc.pair], pc.tile_begin, pc.tile_end);
       ctas[c].item_end = n_items;
     }
-  } else if (total > 0) {
+  } else if (!pairs.empty()) {
     // Streaming cut.  Every item costs its tiles plus a fixed overhead (merge of the
     // warps' partial states, the record or output write, the next Q): ranges are cut to
     // equal COST, so a CTA whose range crosses pair boundaries gets fewer tiles.  The
@@ -254,6 +258,10 @@ static int build_split_plan(const char* who, int tile_tokens, bool bandwidth_sha
     ctas[0].item_begin = 0;
     for (const Pair& pr : pairs) {
       int t = 0;
+      if (pr.tiles == 0) {                                   // an empty key range: one item without tiles
+        items[n_items++] = make_item(pr, 0, 0);
+        cap -= item_cost;
+      }
       while (t < pr.tiles) {
         while (cap <= item_cost && cta + 1 < num_ctas) {  // no room for an item plus a tile: next CTA
           ctas[cta].item_end = n_items;

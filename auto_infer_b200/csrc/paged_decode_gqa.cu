@@ -231,6 +231,14 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       return __ldg(p.block_table + (int64_t)seq * p.bt_stride + lb);
     };
     while (w.item < w.item_end) {
+      if (w.tile >= w.tile_end) {                    // item done (or without any tile: an empty key range)
+        ++w.item;
+        if (w.item < w.item_end) {
+          w.set(na, nb, nc);
+          prefetch_item(w.item + 1);
+        }
+        continue;
+      }
       const int first_lb = (w.tile * kTileTokens) >> p.block_shift;
       const int base = first_lb & ~31;
       if (w.cur.seq != win_seq || base != win_base) {
@@ -276,13 +284,6 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       __syncwarp();
       ++it;
       ++w.tile;
-      if (w.tile >= w.tile_end) {
-        ++w.item;
-        if (w.item < w.item_end) {
-          w.set(na, nb, nc);
-          prefetch_item(w.item + 1);
-        }
-      }
     }
     // drain: do not leave while copies may still land in this CTA's shared memory
     if (lane == 0) {

@@ -45,6 +45,7 @@ class B200GqaBackend(AttentionBackend):
         self.layer_prefix = layer_prefix or (lambda i: f"model.layers.{i}.")
         self.rms_eps = rms_eps
         self.tp_group = tp_group
+        self._meta_pool: dict = {}        # refillable per-step plans, one per head geometry
 
     # -- cache ------------------------------------------------------------
     def alloc_kv_caches(self, num_blocks: int, block_size: int) -> list:
@@ -89,7 +90,8 @@ class B200GqaBackend(AttentionBackend):
     def _attn(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
               ctx) -> torch.Tensor:
         cache = ctx.kv_caches[layer_idx]
-        meta = step_metadata(ctx, self.n_q_heads, self.n_kv_heads, self.head_dim, q.device)
+        meta = step_metadata(ctx, self.n_q_heads, self.n_kv_heads, self.head_dim, q.device,
+                             pool=self._meta_pool)
         out = torch.empty(q.shape[0], self.n_q_heads, self.head_dim, dtype=q.dtype, device=q.device)
         if meta.decode.info.num_items:
             ops.paged_decode_gqa(q, cache[0], cache[1], ctx.block_table, meta.decode, self.scale,

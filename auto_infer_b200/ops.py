@@ -140,7 +140,12 @@ class DecodePlan:
         self.replayable = capacity_seqs is not None
         self.capacity_seqs = max(int(capacity_seqs), len(cu_seqlens_q)) if self.replayable else len(cu_seqlens_q)
         self._nbytes = lib.b200_decode_plan_bytes(self.capacity_seqs, num_kv_heads, self.num_ctas)
-        self.host = torch.empty(self._nbytes // 4, dtype=torch.int32, pin_memory=True)
+        # two pinned staging buffers: a refill writes the one whose last copy has long left
+        self._hosts = [torch.empty(self._nbytes // 4, dtype=torch.int32, pin_memory=True)
+                       for _ in range(2 if self.replayable else 1)]
+        self._copied = [None] * len(self._hosts)
+        self._flip = 0
+        self.host = self._hosts[0]
         self.info = DecodePlanInfo()
         self._build(cu_seqlens_q, seqlens_kv, causal_base)
         used = max(int(self.info.plan_ints), 16)
@@ -150,7 +155,7 @@ class DecodePlan:
         else:
             self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
             ws = (self.info.num_partials * (16 * head_dim + 16)) * 4 + 256
-        self.dev[:used].copy_(self.host[:used], non_blocking=True)
+        self._upload(used)
         self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
 
     def _build(self, cu_seqlens_q, seqlens_kv, causal_base) -> None:
@@ -169,17 +174,27 @@ class DecodePlan:
                                   self.host.data_ptr(), self._nbytes, ctypes.byref(self.info))
         _lib.check(rc, "b200_decode_plan")
 
+    def _upload(self, used: int) -> None:
+        self.dev[:used].copy_(self.host[:used], non_blocking=True)
+        if self.replayable:
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream(self.device))
+            self._copied[self._flip] = done
+
     def refill(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int],
                causal_base: Optional[Sequence[int]] = None) -> None:
-        """Plan another step into the same buffers: host planning, then one pinned ->
-        device copy on the current stream (ahead of the replay that reads it)."""
+        """Plan another step into the same device buffer: host planning into the idle
+        staging buffer, then one pinned -> device copy on the current stream (ahead of
+        the launches or the graph replay that read it).  The kernels of the previous
+        step must be on the same stream (or finished): the copy overwrites their plan."""
         if not self.replayable:
             raise RuntimeError("refill() needs a plan built with capacity_seqs")
-        # the previous copy out of the pinned buffer must have left before it is overwritten
-        torch.cuda.current_stream(self.device).synchronize()
+        self._flip ^= 1
+        self.host = self._hosts[self._flip]
+        if self._copied[self._flip] is not None:
+            self._copied[self._flip].synchronize()      # its copy of two steps ago; normally long done
         self._build(cu_seqlens_q, seqlens_kv, causal_base)
-        used = max(int(self.info.plan_ints), 16)
-        self.dev[:used].copy_(self.host[:used], non_blocking=True)
+        self._upload(max(int(self.info.plan_ints), 16))
 
     @property
     def skipped_seqs(self) -> int:
@@ -395,17 +410,18 @@ def lse_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor,
 
 def cp_exchange_combine(local_record: torch.Tensor, recv_ptrs_dev: int, state: torch.Tensor, rank: int,
                         world: int, rows: int, head_dim: int, out: torch.Tensor,
-                        lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        lse_out: Optional[torch.Tensor] = None, wait_limit_ns: int = 0) -> torch.Tensor:
     """Fused context-parallel exchange + merge: push this rank's packed fp32
     record [o | lse] to every rank's receive buffer over NVLink, wait for all
     ranks' records and merge them into ``out`` (rows, head_dim).  ``recv_ptrs_dev``
-    is the device address of the array of receive-buffer pointers."""
+    is the device address of the array of receive-buffer pointers;
+    ``wait_limit_ns`` bounds the wait for a peer (0 = one second)."""
     _need_cuda(local_record, state, out)
     lib = _lib.load()
     with _on_device(local_record.device):
         rc = lib.b200_cp_exchange_combine(
             local_record.data_ptr(), recv_ptrs_dev, state.data_ptr(), rank, world, rows, head_dim,
-            out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+            int(wait_limit_ns), out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
             lse_out.data_ptr() if lse_out is not None else None,
             status_word(local_record.device).data_ptr(), _stream_ptr(local_record.device))
     _lib.check(rc, "b200_cp_exchange_combine")

@@ -7,20 +7,24 @@ One "step" is one layer-step of the path on the Qwen2.5-72B-shaped long-context
 decode workload (64 q / 8 kv heads, head_dim 128, bf16, 128-token pages, batch
 8, 131072 cached tokens per sequence): KV slot write of the step's token,
 split-KV paged attention and, on N > 1 GPUs (context parallel: every rank holds
-a contiguous 1/N of each sequence's pages), one all-gather of the per-rank
-(o, lse) partials plus the log-sum-exp merge.  Total work is fixed as N grows
-(strong scaling).  The metric is achieved HBM throughput over the algorithmic KV
-bytes of the step, whole job; microseconds per layer-step are reported beside
-it.  Rank 0 prints one JSON line.
+a contiguous 1/N of each sequence's pages), the exchange of the per-rank
+(o, lse) partials fused with the log-sum-exp merge.  Total work is fixed as N
+grows (strong scaling).  The metric is achieved HBM throughput over the
+algorithmic KV bytes of the step, whole job; microseconds per layer-step are
+reported beside it.  Rank 0 prints one JSON line.
 
 ``--impl reference`` times the reference's eager torch attention arithmetic
 (restated for paged KV in oracle/) on the host cores, one sequence of the batch
 per step.
+
+``--case c1|c2|c3|c4|decode --iters N`` runs the kernels of one workload N times
+on a bounded case and exits (what the profiler commands under profiles/ run).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -47,7 +51,7 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--context", type=int, default=CONTEXT)
-    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--no-side-configs", action="store_true",
                     help="skip the kernel-only timings of the smaller configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -55,6 +59,9 @@ def parse_args():
                     help="context-parallel exchange: fused peer-to-peer kernel or NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step's kernels one by one instead of replaying a CUDA graph")
+    ap.add_argument("--case", default=None, choices=["decode", "c1", "c2", "c3", "c4", "merges"],
+                    help="profiler mode: run one workload's kernels --iters times and exit")
+    ap.add_argument("--iters", type=int, default=3)
     return ap.parse_args()
 
 
@@ -140,93 +147,148 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- #
-def time_events(fn, steps, warmup, pre=None):
-    """Per-iteration device times (ms) with CUDA events on the current stream."""
-    for _ in range(warmup):
-        if pre:
-            pre()
-        fn()
-    torch.cuda.synchronize()
+def scale_free_ok(out: torch.Tensor, ref: torch.Tensor, atol_rms=2e-2, rtol=2.0 ** -7, rel_l2=1e-2):
+    """The check the parity tests use for long contexts: error bounds relative to each
+    reference row's own size (the rows are ~0.005 here, far below any absolute tolerance)."""
+    o, r = out.float(), ref.float()
+    rms = r.pow(2).mean(-1, keepdim=True).sqrt()
+    err = (o - r).abs()
+    elem_ok = bool((err <= atol_rms * rms + rtol * r.abs()).all())
+    l2_ok = bool(((o - r).pow(2).sum(-1).sqrt() <= rel_l2 * r.pow(2).sum(-1).sqrt()).all())
+    return elem_ok and l2_ok and bool(torch.isfinite(o).all()) and float(r.abs().max()) > 0
+
+
+def unroll_for(steps: int) -> int:
+    """Layer-steps recorded per CUDA graph: the largest divisor of ``steps`` up to 10 (an
+    engine replays all layers of a model from one graph, not one graph per layer)."""
+    return max(d for d in range(1, 11) if steps % d == 0)
+
+
+def capture_graph(fn, device, reps: int):
+    """Record ``reps`` calls of ``fn`` into one CUDA graph (after eager warm-up calls, so that
+    lazy initialisations happen outside the capture)."""
+    side = torch.cuda.Stream(device=device)
+    side.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream(device).wait_stream(side)
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(reps):
+            fn()
+    torch.cuda.synchronize(device)
+    return graph
+
+
+def timed_batches(run_steps, steps, barrier, n_batches):
+    """Device time (ms) of ``n_batches`` batches of exactly ``steps`` steps, each bracketed by
+    a barrier and a synchronize on both sides."""
     out = []
-    for _ in range(steps):
-        if pre:
-            pre()
+    for _ in range(n_batches):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
         e0.record()
-        fn()
+        run_steps(steps)
         e1.record()
-        torch.cuda.synchronize()
+        barrier()
         out.append(e0.elapsed_time(e1))
     return out
 
 
-def _graph_time(step, flush, iters=40):
-    """Trimmed-mean / best device time (us) of ``step`` replayed from a CUDA graph, L2
-    flushed before every replay (host launch overhead excluded)."""
-    step()
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        step()
-        with torch.cuda.graph(graph, stream=side):
-            step()
-    torch.cuda.synchronize()
-    times = sorted(time_events(graph.replay, iters, 5, pre=flush.zero_))
-    # CUDA event stamps tick every ~2 us on this part: the mean of the middle 60 % resolves
-    # finer than the median of equally quantised samples
-    core = times[len(times) // 5: len(times) - len(times) // 5]
-    return statistics.fmean(core) * 1e3, times[0] * 1e3
+def max_over_ranks(value: float, device, world: int) -> float:
+    if world == 1:
+        return value
+    import torch.distributed as dist
+    t = torch.tensor([value], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
 
-def side_config(name, device, flush):
-    """Kernel-only time of one of the other configurations (slot write +
-    attention), with its roofline fractions against the measured peaks."""
+def layer_rotation_time(make_step, layers, device, reps=12):
+    """Per-layer-step device time (us) of a step replayed from ONE graph over ``layers``
+    distinct caches (as the layers of a model are): graph-launch latency is paid once per
+    model step, consecutive layers overlap their prologues, and every layer's reads come
+    from HBM because the other layers' traffic (far more than L2 holds) passes in between."""
+    steps = [make_step(i) for i in range(layers)]
+
+    def all_layers():
+        for s in steps:
+            s()
+
+    graph = capture_graph(all_layers, device, 1)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize(device)
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize(device)
+        ts.append(e0.elapsed_time(e1) * 1e3 / layers)
+    ts.sort()
+    return statistics.median(ts), ts[0]
+
+
+def side_config(name, device):
+    """Layer-step time of one of the other configurations (slot write + attention) with its
+    roofline fractions against the measured peaks."""
     from auto_infer_b200 import ops, synth
     hbm_peak, _ = measured_peak()
     tensor_peak = measured_tensor_peak()
+    how = "one graph over {} layer caches (reuse distance > L2), time / layers"
     if name.startswith("c3"):
         batch = int(name.split("_b")[1])
         b = synth.config3(batch, device)
         plan = ops.MlaDecodePlan(b.cu_seqlens_q, b.seqlens_kv, 16, device)
         out = torch.empty(b.num_tokens, 16, 512, dtype=torch.bfloat16, device=device)
+        layers = 8
+        caches = [b.kv_cache] + [b.kv_cache.clone() for _ in range(layers - 1)]
 
-        def step():
-            ops.reshape_and_cache(b.k_new, None, b.kv_cache, None, b.slot_mapping)
-            ops.mla_decode_absorbed(b.q, b.kv_cache, b.block_table, plan, b.scale, out=out)
+        def make(i):
+            def step():
+                ops.reshape_and_cache(b.k_new, None, caches[i], None, b.slot_mapping)
+                ops.mla_decode_absorbed(b.q, caches[i], b.block_table, plan, b.scale, out=out)
+            return step
 
-        us, best = _graph_time(step, flush)
+        us, best = layer_rotation_time(make, layers, device)
         bytes_ = sum(b.seqlens_kv) * 1152 + b.num_tokens * 16 * (576 + 512) * 2
         flops = sum(b.seqlens_kv) * 34816
         return {"us_per_layer_step": round(us, 2), "best_us": round(best, 2),
                 "algorithmic_mb": round(bytes_ / 1e6, 2), "achieved_gbs": round(bytes_ / us / 1e3, 1),
                 "hbm_frac": round(bytes_ / us / 1e3 / hbm_peak, 3), "bound": "hbm",
                 "tflops": round(flops / us / 1e6, 1),
-                "tensor_frac": round(flops / us / 1e6 / tensor_peak, 4), "batch": batch}
+                "tensor_frac": round(flops / us / 1e6 / tensor_peak, 4), "batch": batch,
+                "timing": how.format(layers)}
     if name == "c2":
         b = synth.config2(device)
         from auto_infer_b200.metadata import StepMetadata
         meta = StepMetadata(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, device)
         out = torch.empty(b.q.shape, dtype=torch.bfloat16, device=device)
-        k_cache, v_cache = b.kv_cache[0], b.kv_cache[1]
+        layers = 4
+        caches = [b.kv_cache] + [b.kv_cache.clone() for _ in range(layers - 1)]
 
-        def write():
-            ops.reshape_and_cache(b.k_new, b.v_new, k_cache, v_cache, b.slot_mapping)
+        def make_full(i):
+            def step():
+                ops.reshape_and_cache(b.k_new, b.v_new, caches[i][0], caches[i][1], b.slot_mapping)
+                ops.paged_decode_gqa(b.q, caches[i][0], caches[i][1], b.block_table, meta.decode, b.scale, out=out)
+                ops.paged_prefill_gqa(b.q, caches[i][0], caches[i][1], b.block_table, meta.prefill, b.scale, out=out)
+            return step
 
-        def decode():
-            ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, meta.decode, b.scale, out=out)
+        def make_dec(i):
+            return lambda: ops.paged_decode_gqa(b.q, caches[i][0], caches[i][1], b.block_table, meta.decode,
+                                                b.scale, out=out)
 
-        def prefill():
-            ops.paged_prefill_gqa(b.q, k_cache, v_cache, b.block_table, meta.prefill, b.scale, out=out)
+        def make_pre(i):
+            return lambda: ops.paged_prefill_gqa(b.q, caches[i][0], caches[i][1], b.block_table, meta.prefill,
+                                                 b.scale, out=out)
 
-        def step():
-            write()
-            decode()
-            prefill()
-
-        us, best = _graph_time(step, flush)
-        us_dec, _ = _graph_time(decode, flush)
-        us_pre, _ = _graph_time(prefill, flush)
+        us, best = layer_rotation_time(make_full, layers, device)
+        us_dec, _ = layer_rotation_time(make_dec, layers, device)
+        us_pre, _ = layer_rotation_time(make_pre, layers, device)
         # causal-aware flops of the four 512-token chunks over prefixes 0/1024/2048/4096
         flops = sum(4 * 32 * 128 * (512 * p + 131328) for p in (0, 1024, 2048, 4096))
         dec_bytes = sum(b.seqlens_kv[:60]) * 4096 + 2 * 60 * 32 * 128 * 2
@@ -236,21 +298,26 @@ def side_config(name, device, flush):
                 "prefill_chunks_us": round(us_pre, 2), "prefill_gflop": round(flops / 1e9, 2),
                 "prefill_tflops": round(flops / us_pre / 1e6, 1),
                 "prefill_tensor_frac": round(flops / us_pre / 1e6 / tensor_peak, 4),
-                "bound": "tensor (chunks) + hbm (decode rows)", "tokens": b.num_tokens}
+                "bound": "tensor (chunks) + hbm (decode rows)", "tokens": b.num_tokens,
+                "timing": how.format(layers)}
     b = synth.CONFIGS[name]().to(device)
     plan = ops.DecodePlan(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, device)
     out = torch.empty(b.q.shape, dtype=torch.bfloat16, device=device)
+    layers = 8
+    caches = [b.kv_cache] + [b.kv_cache.clone() for _ in range(layers - 1)]
 
-    def step():
-        ops.reshape_and_cache(b.k_new, b.v_new, b.kv_cache[0], b.kv_cache[1], b.slot_mapping)
-        ops.paged_decode_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, plan, b.scale, out=out)
+    def make(i):
+        def step():
+            ops.reshape_and_cache(b.k_new, b.v_new, caches[i][0], caches[i][1], b.slot_mapping)
+            ops.paged_decode_gqa(b.q, caches[i][0], caches[i][1], b.block_table, plan, b.scale, out=out)
+        return step
 
-    us, best = _graph_time(step, flush)
+    us, best = layer_rotation_time(make, layers, device)
     bytes_ = b.kv_bytes() + 2 * b.q.numel() * 2
     return {"us_per_layer_step": round(us, 2), "best_us": round(best, 2),
             "algorithmic_mb": round(bytes_ / 1e6, 2), "achieved_gbs": round(bytes_ / us / 1e3, 1),
             "hbm_frac": round(bytes_ / us / 1e3 / hbm_peak, 3), "bound": "hbm",
-            "batch": len(b.seqlens_kv), "tokens": b.num_tokens}
+            "batch": len(b.seqlens_kv), "tokens": b.num_tokens, "timing": how.format(layers)}
 
 
 def cpu_baseline_sample(args, threads):
@@ -277,7 +344,10 @@ def run_reference(args, rank):
         return orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table,
                                    b.cu_seqlens_q, b.seqlens_kv, b.scale, literal_max_kv=0)
 
-    for _ in range(min(args.warmup, 1)):
+    # each step is a bounded sample (one sequence, ~0.2-1 s of host work): the stated warm-up
+    # and step counts are run as given
+    warmup = max(args.warmup, 1)
+    for _ in range(warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -287,11 +357,11 @@ def run_reference(args, rank):
     sample = f"1 of {args.batch} sequences per step ({args.context} tokens, all 64 heads)"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": dt * 1e3,
         "us_per_layer_step_full_batch": dt * 1e6 * args.batch,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": workload_config(args, 1),
+        "config": workload_config(args, max(args.gpus, 1)),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -309,11 +379,73 @@ def workload_config(args, n):
 
 
 # --------------------------------------------------------------------------- #
+def profile_case(args):
+    """Bounded runs for profilers: the kernels of one workload ``--iters`` times, a 256 MiB
+    fill between iterations so that every iteration reads from HBM."""
+    from auto_infer_b200 import ops, synth
+    from auto_infer_b200.metadata import StepMetadata
+    dev = torch.device("cuda", 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    batch = args.batch or 1
+    if args.case == "merges":
+        # the two stand-alone merge kernels on config-5-sized records (8 ranks x 512 rows x 128)
+        g = torch.Generator(device=dev).manual_seed(1)
+        o = torch.randn(8, 512, 128, generator=g, device=dev)
+        lse = torch.randn(8, 512, generator=g, device=dev)
+        name = "lse_combine on 8 x 512 x 128 records"
+
+        def step():
+            ops.lse_combine(o, lse)
+    elif args.case == "c3":
+        b = synth.config3(batch if args.batch else 64, dev)
+        name = b.name
+        plan = ops.MlaDecodePlan(b.cu_seqlens_q, b.seqlens_kv, 16, dev)
+        out = torch.empty(b.num_tokens, 16, 512, dtype=torch.bfloat16, device=dev)
+
+        def step():
+            ops.reshape_and_cache(b.k_new, None, b.kv_cache, None, b.slot_mapping)
+            ops.mla_decode_absorbed(b.q, b.kv_cache, b.block_table, plan, b.scale, out=out)
+    else:
+        if args.case == "decode":
+            b = synth.config5(dev, context=args.context, batch=batch)
+        elif args.case == "c2":
+            b = synth.config2(dev)
+        else:
+            b = synth.CONFIGS[args.case]().to(dev)
+        name = b.name
+        meta = StepMetadata(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, dev)
+        out = torch.empty(b.q.shape, dtype=torch.bfloat16, device=dev)
+
+        def step():
+            ops.reshape_and_cache(b.k_new, b.v_new, b.kv_cache[0], b.kv_cache[1], b.slot_mapping)
+            ops.paged_decode_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, meta.decode,
+                                 b.scale, out=out)
+            if meta.prefill is not None:
+                ops.paged_prefill_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, meta.prefill,
+                                      b.scale, out=out)
+    for _ in range(args.iters):
+        flush.zero_()
+        step()
+    torch.cuda.synchronize()
+    status = ops.read_status(dev)
+    print(f"{name}: {args.iters} iterations, status {status}")
+    if status:
+        raise SystemExit(1)
+
+
+# --------------------------------------------------------------------------- #
 def main():
     args = parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.case:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py --case needs a CUDA device")
+        profile_case(args)
+        return
+    if args.batch is None:
+        args.batch = BATCH
     if args.impl == "reference":
         run_reference(args, rank)
         return
@@ -332,11 +464,10 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        # NCCL prints its version banner to stdout at VERSION/INFO level; rank 0's stdout must
-        # carry the JSON line only
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE") and \
-                not os.environ.get("B200_BENCH_KEEP_NCCL_DEBUG"):
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # NCCL's own log (NCCL_DEBUG as the caller set it) goes to stderr, so that rank 0's
+        # stdout carries the JSON line only
+        if os.environ.get("NCCL_DEBUG") and not os.environ.get("NCCL_DEBUG_FILE"):
+            os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
         dist.init_process_group("nccl", device_id=device)
 
     # ---- workload: this rank's slice of every sequence's pages -------------
@@ -364,69 +495,171 @@ def main():
         if owner_of_new_token:
             ops.reshape_and_cache(b.k_new, b.v_new, k_cache, v_cache, b.slot_mapping)
 
-    # the layer-step (slot write, attention, all-gather, merge) is recorded once into a
-    # CUDA graph and replayed: the engine's graph mode does the same for whole decode steps
-    graph = None
-    if not args.no_graph:
-        graph = cpd.capture(b.q, k_cache, v_cache, b.block_table, b.scale, before=write_new_token)
-
-    def step():
-        if graph is not None:
-            graph.replay()
-            return cpd.out
+    def layer_step():
         write_new_token()
         return cpd.attend(b.q, k_cache, v_cache, b.block_table, b.scale)
+
+    def decode_only():
+        if world > 1:
+            ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, cpd.meta.decode, b.scale,
+                                 out=cpd.partial.o, lse_out=cpd.partial.lse)
+        else:
+            ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, cpd.meta.decode, b.scale, out=cpd.out)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Layer-steps are recorded into CUDA graphs of `unroll` steps each and replayed: the
+    # engine's graph mode replays all layers of a model from one graph the same way.
+    unroll = 1 if args.no_graph else unroll_for(args.steps)
+    barrier()                                       # ranks lined up before the first exchange
+    graph = None if args.no_graph else capture_graph(layer_step, device, unroll)
+    kgraph = None if args.no_graph else capture_graph(decode_only, device, unroll)
+
+    def run_steps(n):
+        if graph is None:
+            for _ in range(n):
+                layer_step()
+        else:
+            for _ in range(n // unroll):
+                graph.replay()
+
+    def run_kernel(n):
+        if kgraph is None:
+            for _ in range(n):
+                decode_only()
+        else:
+            for _ in range(n // unroll):
+                kgraph.replay()
+
     total_kv_bytes = args.batch * args.context * 2 * b.n_kv * b.head_dim * 2
     local_kv_bytes = b.kv_bytes()
 
-    # ---- timed region: K steps, device events, max over ranks --------------
-    for _ in range(max(args.warmup, 3)):
-        step()
+    # ---- timed region: batches of exactly K steps, device events, max over ranks --------
+    warm = max(args.warmup, 3)
+    barrier()
+    run_steps(unroll * math.ceil(warm / unroll))
+    barrier()
+    probe = timed_batches(run_steps, args.steps, barrier, 1)[0]
+    # enough batches for half a second of timed work (clock samples come every 20 ms)
+    n_batches = int(min(200, max(10, math.ceil(500.0 / max(probe, 1e-3)))))
+    if world > 1:
+        nb = torch.tensor([n_batches], device=device)
+        dist.all_reduce(nb, op=dist.ReduceOp.MAX)
+        n_batches = int(nb.item())
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)                      # let the sampler come up before the timed region
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    barrier()
-    elapsed_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    ms_per_step = elapsed_ms / args.steps
+    batches = timed_batches(run_steps, args.steps, barrier, n_batches)
+    ms_per_step = max_over_ranks(statistics.median(batches), device, world) / args.steps
     value = total_kv_bytes / (ms_per_step * 1e-3) / 1e12
-    launches_per_step = (1 if owner_of_new_token else 0) + 1 + \
-        (1 if cpd.meta.decode.info.num_multi else 0) + (1 if world > 1 else 0)
+    launches_per_step = (1 if owner_of_new_token else 0) + 1 + (1 if world > 1 else 0)
 
-    # ---- dominant kernel alone (decode + its merge), for the roofline -------
-    if world > 1:
-        out32 = cpd.partial
-        kern = lambda: ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, cpd.meta.decode,
-                                            b.scale, out=out32.o, lse_out=out32.lse)
-    else:
-        kern = lambda: ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, cpd.meta.decode,
-                                            b.scale, out=cpd.out)
-    ktimes = time_events(kern, args.steps, 3)
-    kernel_ms = sum(ktimes) / len(ktimes)
-    if world > 1:
-        t = torch.tensor([kernel_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        kernel_ms = float(t.item())
+    # ---- the dominant kernel alone, replayed the same way, for the roofline -------------
+    run_kernel(unroll * 2)
+    kbatches = timed_batches(run_kernel, args.steps, barrier, max(5, n_batches // 4))
+    my_kernel_ms = statistics.median(kbatches) / args.steps
+    kernel_ms = max_over_ranks(my_kernel_ms, device, world)
+    clocks = sampler.stop() if rank == 0 else None
     peak, peak_kind = measured_peak()
     algorithmic = local_kv_bytes + 2 * b.q.numel() * 2
     achieved = algorithmic / (kernel_ms * 1e-3) / 1e9
     traffic = ncu_traffic("c5") if world == 1 else None
+
+    # ---- where a context-parallel step's time goes (per rank) ---------------------------
+    breakdown = None
+    if world > 1:
+        def exchange_only():
+            if exchange is not None:
+                ops.cp_exchange_combine(cpd.partial.flat, exchange.recv_ptrs_dev, exchange.state, rank, world,
+                                        cpd.partial.rows, cpd.partial.head_dim, cpd.out.view(cpd.partial.rows, -1))
+            else:
+                from auto_infer_b200.context_parallel import all_gather_partials, split_gathered
+                gathered = all_gather_partials(cpd.partial.flat, None)
+                o_parts, lse_parts = split_gathered(gathered, cpd.partial.rows, cpd.partial.head_dim)
+                ops.lse_combine(o_parts, lse_parts, out=cpd.out.view(cpd.partial.rows, -1))
+
+        barrier()
+        xgraph = exchange_only if args.no_graph else capture_graph(exchange_only, device, unroll)
+
+        def run_exchange(n):
+            if args.no_graph:
+                for _ in range(n):
+                    exchange_only()
+            else:
+                for _ in range(n // unroll):
+                    xgraph.replay()
+
+        run_exchange(unroll * 2)
+        xb = timed_batches(run_exchange, args.steps, barrier, 5)
+        my_exchange_us = statistics.median(xb) / args.steps * 1e3
+        write_us = 0.0
+        if owner_of_new_token:
+            wgraph = capture_graph(write_new_token, device, unroll)
+            torch.cuda.synchronize()
+            wt = []
+            for _ in range(5):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.steps // unroll):
+                    wgraph.replay()
+                e1.record()
+                torch.cuda.synchronize()
+                wt.append(e0.elapsed_time(e1) / args.steps * 1e3)
+            write_us = statistics.median(wt)
+        mine = torch.tensor([my_kernel_ms * 1e3, my_exchange_us, write_us], device=device, dtype=torch.float64)
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        dec = [round(float(t[0]), 2) for t in allr]
+        breakdown = {"decode_us_per_rank": dec,
+                     "decode_us_spread": round(max(dec) - min(dec), 2),
+                     "exchange_us_per_rank": [round(float(t[1]), 2) for t in allr],
+                     "write_us_owner_rank": round(float(allr[-1][2]), 2),
+                     "step_us": round(ms_per_step * 1e3, 2),
+                     "note": "each leg replayed alone from its own graph; the exchange leg contains "
+                             "the wait for the slowest peer of that leg"}
+
+    # ---- does the timed computation give the right rows?  (untimed) ---------------------
+    verified, verify_how = None, None
+    try:
+        if world == 1:
+            from oracle import paged_attention_oracle as orc
+            run_steps(unroll)
+            torch.cuda.synchronize()
+            seq = 0
+            ids = b.block_table[seq].long()
+            bt = torch.arange(ids.numel(), dtype=torch.int32)[None]
+            torch.set_num_threads(os.cpu_count() or 1)
+            ref = orc.paged_attention(b.q[seq:seq + 1].cpu(), k_cache[ids].cpu(), v_cache[ids].cpu(), bt, [1],
+                                      [b.seqlens_kv[seq]], b.scale, literal_max_kv=0)
+            verified = scale_free_ok(cpd.out[seq:seq + 1].cpu(), ref)
+            verify_how = "sequence 0 of the timed step against the CPU oracle, row-relative tolerance"
+        else:
+            # sequence 0's pages of every rank are gathered on rank 0, which runs the
+            # single-GPU kernel over the whole sequence and compares the rows
+            run_steps(unroll)
+            torch.cuda.synchronize()
+            ids = b.block_table[0].long()
+            mine_k, mine_v = k_cache[ids].contiguous(), v_cache[ids].contiguous()
+            ks = [torch.empty_like(mine_k) for _ in range(world)] if rank == 0 else None
+            vs = [torch.empty_like(mine_v) for _ in range(world)] if rank == 0 else None
+            dist.gather(mine_k, ks, dst=0)
+            dist.gather(mine_v, vs, dst=0)
+            if rank == 0:
+                full_k, full_v = torch.cat(ks), torch.cat(vs)
+                bt = torch.arange(full_k.shape[0], dtype=torch.int32, device=device)[None]
+                plan1 = ops.DecodePlan([1], [args.context], b.n_q, b.n_kv, device)
+                one = ops.paged_decode_gqa(b.q[0:1], full_k, full_v, bt, plan1, b.scale, out_f32=True)
+                torch.cuda.synchronize()
+                verified = scale_free_ok(cpd.out[0:1], one)
+                verify_how = (f"sequence 0: the {world}-rank result against the single-GPU kernel run on "
+                              "rank 0 over the gathered pages, row-relative tolerance")
+                del full_k, full_v, ks, vs
+    except Exception as exc:                  # verification must never take the measurement down
+        verify_how = f"verification did not run: {exc!r}"
 
     # ---- end to end through the backend call with host buffers -------------
     backend = B200GqaBackend(b.n_q, b.n_kv, b.head_dim, b.scale, 1, device, torch.bfloat16)
@@ -454,47 +687,42 @@ def main():
     d2h = out_host.numel() * out_host.element_size()
 
     def e2e_step():
+        # a step as the engine drives it: inputs from the host, this step's lengths planned on
+        # the host (into buffers the backend keeps), kernels, result back to the host
         dev_arena.copy_(host_arena, non_blocking=True)
         if world == 1:
             ctx = ForwardContext(None, None, dev["slot_mapping"], dev["block_table"],
                                  b.cu_seqlens_q, b.seqlens_kv, None, backend, [b.kv_cache], True)
             o = backend.paged_attention(0, dev["q"], dev["k_new"], dev["v_new"], ctx)
         else:
-            plan = ContextParallelDecode(b.cu_seqlens_q, global_kv, b.n_q, b.n_kv, b.head_dim,
-                                         b.block_size, device, cp_rank=rank, cp_size=world,
-                                         exchange=exchange)
+            cpd.replan(b.cu_seqlens_q, global_kv)
             if owner_of_new_token:
                 ops.reshape_and_cache(dev["k_new"], dev["v_new"], k_cache, v_cache, dev["slot_mapping"])
-            o = plan.attend(dev["q"], k_cache, v_cache, dev["block_table"], b.scale)
+            o = cpd.attend(dev["q"], k_cache, v_cache, dev["block_table"], b.scale)
         out_host.copy_(o, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
         e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_runs = []
+    for _ in range(5):
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        barrier()
+        e2e_runs.append((time.perf_counter() - t0) * 1e3 / args.steps)
+    e2e_ms = max_over_ranks(statistics.median(e2e_runs), device, world)
     e2e_value = total_kv_bytes / (e2e_ms * 1e-3) / 1e12
     status = ops.read_status(device)
-    # the sampler ran from before the timed region to the end of the end-to-end loop
-    clocks = sampler.stop() if rank == 0 else None
 
     # ---- smaller configurations and the CPU baseline (rank 0, N = 1) --------
     side, cpu = {}, None
     if rank == 0 and world == 1:
         if not args.no_side_configs:
-            flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
             for name in ("c1", "c2", "c3_b4", "c3_b16", "c3_b64", "c4"):
-                side[name] = side_config(name, device, flush)
+                side[name] = side_config(name, device)
                 torch.cuda.empty_cache()
-            del flush
         if not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             cb, orc = cpu_baseline_sample(args, threads)
@@ -513,33 +741,38 @@ def main():
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "warmup": warm, "ms_per_step": ms_per_step,
             "us_per_layer_step": ms_per_step * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "config": dict(workload_config(args, world), exchange=exchange_kind),
+            "timing": {"batches": n_batches, "steps_per_batch": args.steps, "reported": "median batch",
+                       "layer_steps_per_graph": unroll if not args.no_graph else 0,
+                       "batch_ms_min": min(batches), "batch_ms_max": max(batches)},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
-                         "kernel": "paged_decode_gqa_kernel (+ decode_merge_kernel, one C call)",
+                         "kernel": "paged_decode_gqa_kernel (cut pairs merged in-kernel)",
                          "kernel_us": kernel_ms * 1e3, "algorithmic_bytes": algorithmic,
-                         "frac_of_nominal_8tbs": achieved / 8000.0},
+                         "frac_of_nominal_8tbs": achieved / 8000.0,
+                         "timed": "same graph replay as the step, the attention kernel alone"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "device_status": status,
+            "verified": verified, "verified_how": verify_how,
         }
+        if breakdown is not None:
+            line["cp_breakdown"] = breakdown
         if cpu is not None:
             line["cpu_baseline"] = cpu
         if side:
             line["other_configs"] = side
         print(json.dumps(line), flush=True)
     if world > 1:
-        # Tear down in dependency order: a CUDA graph that recorded NCCL kernels has to go
-        # before its communicator, and the exit must not wait on peers that already left.
-        graph = None
+        # graphs first (they hold the kernels' arguments), then the communicator
+        graph = kgraph = None
         torch.cuda.synchronize()
         dist.barrier()
-        sys.stdout.flush()
-        os._exit(0)
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -300,19 +300,25 @@ int b200_lse_combine(const float* o_parts, const float* lse_parts,
  * reference, whose only CP code all-gathers K and V per layer,
  * auto_infer/models/qwen2.py:211-212).  Every rank pushes its packed fp32
  * record [o (rows*D) | lse (rows)] into the receive buffers of all ranks with
- * peer-to-peer stores, raises a step flag, waits at most one second for the
- * flags of all ranks and merges the records from its own memory.
+ * peer-to-peer stores, raises flags there, waits for the flags of all ranks in
+ * its own buffer and merges the records from its own memory.  The rows are
+ * dealt to the blocks of the grid; a block waits only for the same block of the
+ * peers.
  *   recv_ptrs_dev: device array of `world` pointers, entry r = base of rank r's
  *     receive buffer as mapped in this process (symmetric memory; the caller
  *     sets it up, zero-filled, b200_cp_exchange_buffer_bytes() bytes per rank)
  *   state_dev: 4 uint32 of local device memory, zero-filled once
- * All ranks must call it once per step with the same shapes.  A missing peer
- * sets B200_STATUS_WAIT_TIMEOUT and leaves `out` unwritten. */
+ *   wait_limit_ns: how long a block waits for a peer's flag; 0 = one second.
+ *     When it runs out the block sets B200_STATUS_WAIT_TIMEOUT and leaves its
+ *     rows of `out` unwritten; the step number still advances, so the next call
+ *     starts a fresh step.  Ranks should therefore be lined up (a host barrier
+ *     after set-up) before the first exchange.
+ * All ranks must call it once per step with the same shapes. */
 size_t b200_cp_exchange_buffer_bytes(int world, int64_t rows, int head_dim);
 
 int b200_cp_exchange_combine(const float* local_record, const uint64_t* recv_ptrs_dev,
                              uint32_t* state_dev, int rank, int world,
-                             int64_t rows, int head_dim,
+                             int64_t rows, int head_dim, int64_t wait_limit_ns,
                              void* out, int out_is_f32, float* lse_out,
                              int32_t* status, void* stream);
 

@@ -31,7 +31,7 @@ def test_emulated_ranks_merge_to_the_unsplit_answer(ranks):
         local_bt = cp.shard_block_table(d.block_table, b.seqlens_kv, 128, r, ranks)
         plan = ops.DecodePlan(b.cu_seqlens_q, local_kv, b.n_q, b.n_kv, "cuda", causal_base=base)
         buf = cp.PartialBuffer(b.num_tokens, b.n_q, b.head_dim, "cuda")
-        buf.clear()
+        buf.flat.fill_(float("nan"))       # rows a rank has no keys for are written too (zeros, lse -inf)
         ops.paged_decode_gqa(d.q, d.kv_cache[0], d.kv_cache[1], local_bt, plan, b.scale,
                              out=buf.o, lse_out=buf.lse)
         gathered[r].copy_(buf.flat)
@@ -41,6 +41,50 @@ def test_emulated_ranks_merge_to_the_unsplit_answer(ranks):
     assert_attention_close(out.view_as(ref).cpu(), ref, lse.view_as(ref_lse).cpu(), ref_lse,
                            f"{ranks} emulated ranks")
     assert ops.read_status("cuda") == 0
+
+
+def test_exchange_wait_for_an_absent_peer_runs_out_and_the_next_step_works():
+    """The fused exchange waits for its peers with a limit.  Two 'ranks' share this GPU, each
+    with its own receive buffer and step counter, and run one after the other, so the first
+    caller of a step never finds its peer's flag: its wait runs out (20 ms here), it reports
+    B200_STATUS_WAIT_TIMEOUT and leaves `out` alone, and the context stays usable.  The rank
+    that calls second finds both records and merges them."""
+    from auto_infer_b200 import _lib, ops
+    lib = _lib.load()
+    rows, dim, world = 40, 128, 2
+    g = torch.Generator().manual_seed(5)
+    nfloats = lib.b200_cp_exchange_buffer_bytes(world, rows, dim) // 4
+    bufs = [torch.zeros(nfloats, dtype=torch.float32, device="cuda") for _ in range(world)]
+    ptrs = torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device="cuda")
+    states = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    limit_ns = 20_000_000
+
+    def record(step, rank):
+        o = torch.randn(rows, dim, generator=g)
+        lse = torch.randn(rows, generator=g) * 3
+        return torch.cat([o.reshape(-1), lse]).cuda(), o, lse
+
+    def call(rank, rec, out):
+        return ops.cp_exchange_combine(rec, ptrs.data_ptr(), states[rank], rank, world, rows, dim, out,
+                                       wait_limit_ns=limit_ns)
+
+    ops.read_status("cuda")
+    for step in range(2):                      # both receive slots
+        recs = [record(step, r) for r in range(world)]
+        want, _ = orc.lse_combine(torch.stack([recs[0][1], recs[1][1]]), torch.stack([recs[0][2], recs[1][2]]),
+                                  out_dtype=torch.float32)
+        first, second = (0, 1) if step == 0 else (1, 0)
+        out_first = torch.full((rows, dim), 7.0, dtype=torch.float32, device="cuda")
+        call(first, recs[first][0], out_first)
+        torch.cuda.synchronize()
+        assert ops.read_status("cuda") == _lib.STATUS_WAIT_TIMEOUT
+        assert torch.equal(out_first, torch.full_like(out_first, 7.0))        # nothing merged, nothing written
+        out_second = torch.zeros(rows, dim, dtype=torch.float32, device="cuda")
+        call(second, recs[second][0], out_second)
+        torch.cuda.synchronize()
+        assert ops.read_status("cuda") == 0
+        torch.testing.assert_close(out_second.cpu(), want, atol=1e-5, rtol=1e-5)
+    assert [int(s[0]) for s in states] == [2, 2]                              # both ranks are at step 2
 
 
 def _nccl_worker(rank, world, port, ret, use_p2p=False):
