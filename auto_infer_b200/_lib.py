@@ -74,6 +74,16 @@ SIGNATURES = {
     "b200_cp_exchange_combine": (c_int, [
         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int64,
         c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_gqa_rope_cache": (c_int, [
+        c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+        c_void_p, c_void_p, c_float, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200_mla_rope_norm_cache": (c_int, [
+        c_void_p, c_int64, c_void_p, c_float, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64,
+        c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200_copy_blocks": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "b200_lse_combine": (c_int, [
         c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int,
         c_void_p, c_int, c_void_p, c_void_p]),

@@ -24,6 +24,8 @@ SOURCES = [
     "mla_decode.cu",
     "lse_combine.cu",
     "cp_exchange.cu",
+    "copy_blocks.cu",
+    "rope_cache.cu",
 ]
 
 NVCC_FLAGS = [

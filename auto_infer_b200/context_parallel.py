@@ -147,8 +147,6 @@ class ContextParallelDecode:
         self.meta = StepMetadata(cu_seqlens_q, self.local_kv, num_q_heads, num_kv_heads, head_dim,
                                  device, causal_base=self.bases,
                                  capacity_seqs=capacity_seqs or len(cu_seqlens_q))
-        if self.meta.prefill_seqs:
-            raise NotImplementedError("context-parallel attention is built for decode-shaped rows")
         self.num_tokens = self.meta.num_tokens
         self.partial = PartialBuffer(self.num_tokens, num_q_heads, head_dim, device)
         self.out = torch.empty(self.num_tokens, num_q_heads, head_dim, dtype=torch.bfloat16,
@@ -162,8 +160,6 @@ class ContextParallelDecode:
         self.local_kv, self.offsets, self.bases = shard_lengths(
             seqlens_kv_global, cu_seqlens_q, self.block_size, self.cp_rank, self.cp_size)
         self.meta.rebuild(cu_seqlens_q, self.local_kv, causal_base=self.bases)
-        if self.meta.prefill_seqs:
-            raise NotImplementedError("context-parallel attention is built for decode-shaped rows")
 
     def capture(self, q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                 local_block_table: torch.Tensor, scale: float, before=None):
@@ -192,15 +188,29 @@ class ContextParallelDecode:
         torch.cuda.synchronize(q.device)
         return graph
 
+    def _local(self, q, key_cache, value_cache, local_block_table, scale, out, lse_out=None):
+        """This rank's attention over its own pages: decode-shaped rows through the split-KV
+        kernel, wide query blocks (prefill chunks) through the tensor-core kernel.  Both take
+        the causal base in local coordinates and write zeros / lse = -inf for rows that see
+        none of this rank's keys, so every row of ``out`` is written."""
+        if self.meta.decode.info.num_items or self.meta.decode.replayable:
+            ops.paged_decode_gqa(q, key_cache, value_cache, local_block_table, self.meta.decode, scale,
+                                 out=out, lse_out=lse_out)
+        if self.meta.prefill is not None:
+            ops.paged_prefill_gqa(q, key_cache, value_cache, local_block_table, self.meta.prefill, scale,
+                                  out=out, lse_out=lse_out)
+
     def attend(self, q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                local_block_table: torch.Tensor, scale: float) -> torch.Tensor:
-        """One layer-step: local attention -> all-gather -> merge.  Returns the
-        bf16 (T, Hq, D) output, identical on every rank."""
+        """One layer-step: local attention -> exchange -> merge.  Returns the bf16
+        (T, Hq, D) output, identical on every rank.  Handles decode rows, multi-token
+        verify rows and prefill chunks alike: where the reference's context-parallel
+        prefill all-gathers K and V per layer (auto_infer/models/qwen2.py:181-226), the
+        ranks here exchange T*Hq*(D+1) floats whatever the context length."""
         if self.cp_size == 1:
-            return ops.paged_decode_gqa(q, key_cache, value_cache, local_block_table,
-                                        self.meta.decode, scale, out=self.out)
-        ops.paged_decode_gqa(q, key_cache, value_cache, local_block_table, self.meta.decode, scale,
-                             out=self.partial.o, lse_out=self.partial.lse)
+            self._local(q, key_cache, value_cache, local_block_table, scale, self.out)
+            return self.out
+        self._local(q, key_cache, value_cache, local_block_table, scale, self.partial.o, self.partial.lse)
         if self.exchange is not None:
             # one kernel: peer-to-peer push of [o | lse], flag wait, merge
             ops.cp_exchange_combine(self.partial.flat, self.exchange.recv_ptrs_dev, self.exchange.state,

@@ -204,7 +204,7 @@ static int build_split_plan(const char* who, int tile_tokens, bool bandwidth_sha
     }
     if (q_len == 0) continue;
     if (q_len * group > kMaxRows) {
-      if (kv_lens[b] > 0) ++skipped;
+      ++skipped;
       continue;
     }
     // A sequence without keys (the empty slice of a context-parallel rank) still gets an

@@ -701,7 +701,9 @@ extern "C" int b200_prefill_plan(const int32_t* cu_q, const int32_t* kv_lens,
       return B200_EINVAL;
     }
     const int rows = q_len * group;
-    if (q_len == 0 || kv_lens[b] == 0 || rows <= min_rows) continue;
+    // a sequence without keys (the empty slice of a context-parallel rank) is planned too:
+    // its items have no tile and come out as zeros with lse = -inf
+    if (q_len == 0 || rows <= min_rows) continue;
     const int base = causal_base ? causal_base[b] : kv_lens[b] - q_len;
     for (int row0 = 0; row0 < rows; row0 += kPfRows) {
       const int last_row = std::min(row0 + kPfRows, rows) - 1;

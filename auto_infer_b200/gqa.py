@@ -6,9 +6,12 @@ from __future__ import annotations
 
 import torch
 
+from contextlib import nullcontext
+from dataclasses import dataclass
+
 from . import ops
 from .base import AttentionBackend, _lin
-from .metadata import step_metadata
+from .metadata import StepMetadata, cached_step_metadata, step_metadata
 
 
 def rotate_half(x: torch.Tensor) -> torch.Tensor:
@@ -60,23 +63,24 @@ class B200GqaBackend(AttentionBackend):
 
     # -- whole sub-block ----------------------------------------------------
     def attention(self, layer_idx: int, x: torch.Tensor, ctx) -> torch.Tensor:
+        """The sub-block of auto_infer/layers/attention/gqa.py:27-49 (its wiring is the plug-in
+        contract): packed QKV projection, optional QK RMSNorm, NeoX RoPE, slot write, paged
+        attention, o_proj, tensor-parallel all-reduce.  Everything between the two GEMMs
+        runs in two launches here: the fused prologue (norm + RoPE + slot write) and the
+        attention kernel."""
         t = x.shape[0]
         n_q, n_kv, hd = self.n_q_heads, self.n_kv_heads, self.head_dim
         w = self.w
         p = self.layer_prefix(layer_idx) + "self_attn."
         qkv = _lin(x, w[p + "qkv_proj.weight"], w.get(p + "qkv_proj.bias"))
         q, k, v = qkv.split((n_q * hd, n_kv * hd, n_kv * hd), dim=-1)
-        q = q.view(t, n_q, hd)
-        k = k.view(t, n_kv, hd)
-        v = v.view(t, n_kv, hd)
+        cache = ctx.kv_caches[layer_idx]
         qn = w.get(p + "q_norm.weight")
-        if qn is not None:
-            q = rms_norm(q, qn, self.rms_eps)
-            k = rms_norm(k, w[p + "k_norm.weight"], self.rms_eps)
-        q = q * ctx.cos + rotate_half(q) * ctx.sin
-        k = k * ctx.cos + rotate_half(k) * ctx.sin
-        self._write_kv(layer_idx, k, v, ctx)
-        o = self._attn(layer_idx, q, k, v, ctx).reshape(t, n_q * hd)
+        q = ops.gqa_rope_cache(q.view(t, n_q, hd), k.view(t, n_kv, hd), v.view(t, n_kv, hd), ctx.cos, ctx.sin,
+                               cache[0], cache[1], ctx.slot_mapping, q_norm_weight=qn,
+                               k_norm_weight=w[p + "k_norm.weight"] if qn is not None else None,
+                               eps=self.rms_eps if self.rms_eps is not None else 1e-6)
+        o = self._attn(layer_idx, q, None, None, ctx).reshape(t, n_q * hd)
         out = _lin(o, w[p + "o_proj.weight"])
         if self.tp_group is not None and torch.distributed.get_world_size(self.tp_group) > 1:
             torch.distributed.all_reduce(out, group=self.tp_group)
@@ -107,3 +111,106 @@ class B200GqaBackend(AttentionBackend):
         q/k/v: the part of ``attention`` this package accelerates."""
         self._write_kv(layer_idx, k, v, ctx)
         return self._attn(layer_idx, q, k, v, ctx)
+
+
+@dataclass(frozen=True)
+class _GraphRegistration:
+    """One captured attention call: the refillable plan its launch reads and the static
+    tensors it was recorded against (the counterpart of ``_FiaRegistration``,
+    auto_infer/layers/attention/graph_fia.py:6-14)."""
+    meta: StepMetadata
+    layer_idx: int
+    query: torch.Tensor
+    output: torch.Tensor
+    block_size: int
+
+
+class B200GraphGqaBackend(B200GqaBackend):
+    """Graph-capturable variant, the counterpart of ``GraphGqaBackend`` +
+    ``GraphFiaLifecycle`` (auto_infer/layers/attention/gqa.py:134-226,
+    graph_fia.py:17-104) with the attributes the graph runners touch: ``capturing``,
+    ``reg``, ``begin_capture() / end_capture()``, ``update() / update_registrations() /
+    update_many()``, ``supports_prefill_graph``.
+
+    The reference re-issues every layer's attention task on the host before each replay,
+    because its vendor op takes the step's length lists as host arguments.  Here a captured
+    launch reads lengths and work list from a plan at a fixed device address, so an update
+    is ONE refill of that plan (host planning + one small copy) for all layers of the graph.
+
+    Capture protocol (what the reference's runners do, worker/graph_decode_runner.py
+    ``_capture``): run the step once eagerly with the context the capture will use
+    (``capturing`` False) - that is when the plan's buffers are allocated - then
+    ``begin_capture()``, record the step with the same context object, ``end_capture()``.
+    The plan the capture used is taken out of the backend's pool and belongs to the graph
+    from then on (``gear.reg = backend.reg``)."""
+
+    supports_prefill_graph = False      # wide query blocks run eagerly; their launch is sized by the step
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.capturing = False
+        self.reg: list = []
+
+    def alloc_kv_caches(self, num_blocks: int, block_size: int) -> list:
+        """Per layer TWO tensors (k, v), each (num_blocks, block_size, n_kv, head_dim), as
+        gqa.py:192-200 (the runner passes num_blocks + its scratch blocks)."""
+        if self.dtype != torch.bfloat16:
+            raise NotImplementedError("the B200 kernels are built for bf16 caches")
+        shape = (num_blocks, block_size, self.n_kv_heads, self.head_dim)
+        return [(torch.zeros(shape, device=self.device, dtype=self.dtype),
+                 torch.zeros(shape, device=self.device, dtype=self.dtype))
+                for _ in range(self.num_layers)]
+
+    # -- lifecycle (graph_fia.py:63-68) --------------------------------------
+    def begin_capture(self) -> None:
+        self.capturing = True
+        self.reg = []
+
+    def end_capture(self) -> None:
+        self.capturing = False
+
+    def _attn(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+              ctx) -> torch.Tensor:
+        if not self.capturing:
+            return super()._attn(layer_idx, q, k, v, ctx)
+        meta = cached_step_metadata(ctx, self.n_q_heads, self.n_kv_heads, self.head_dim, q.device)
+        if meta is None or not meta.decode.replayable:
+            raise RuntimeError(
+                "capture needs one eager step with the same context first (capturing False): the "
+                "plan's buffers cannot be allocated while the stream is being captured")
+        if meta.prefill is not None:
+            raise NotImplementedError("wide query blocks (prefill chunks) are not captured; "
+                                      "supports_prefill_graph is False")
+        for key, pooled in list(self._meta_pool.items()):
+            if pooled is meta:                      # the plan now belongs to this capture
+                del self._meta_pool[key]
+        cache = ctx.kv_caches[layer_idx]
+        out = torch.empty(q.shape[0], self.n_q_heads, self.head_dim, dtype=q.dtype, device=q.device)
+        ops.paged_decode_gqa(q, cache[0], cache[1], ctx.block_table, meta.decode, self.scale, out=out)
+        self.reg.append(_GraphRegistration(meta, layer_idx, q, out, cache[0].shape[1]))
+        return out
+
+    # -- per-step update (graph_fia.py:87-104) --------------------------------
+    @staticmethod
+    def _refill(meta: StepMetadata, ctx, stream) -> None:
+        with (torch.cuda.stream(stream) if stream is not None else nullcontext()):
+            meta.rebuild(ctx.cu_seqlens_q, ctx.seqlens_kv)
+
+    def update(self, ctx, stream=None) -> None:
+        self.update_registrations(self.reg, ctx, stream)
+
+    def update_registrations(self, registrations, ctx, stream=None) -> None:
+        seen = set()
+        for registration in registrations:
+            if id(registration.meta) not in seen:
+                seen.add(id(registration.meta))
+                self._refill(registration.meta, ctx, stream)
+
+    def update_many(self, contexts, stream=None) -> None:
+        if len(contexts) != len(self.reg):
+            raise ValueError("graph-task contexts must match registrations")
+        seen = set()
+        for ctx, registration in zip(contexts, self.reg):
+            if id(registration.meta) not in seen:
+                seen.add(id(registration.meta))
+                self._refill(registration.meta, ctx, stream)

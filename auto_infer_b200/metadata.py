@@ -44,7 +44,7 @@ class StepMetadata:
         prev = 0
         self.prefill_seqs = []
         for b, end in enumerate(self.cu_seqlens_q):
-            if (end - prev) * group > 16 and self.seqlens_kv[b] > 0:
+            if (end - prev) * group > 16:
                 self.prefill_seqs.append(b)
             prev = end
 
@@ -67,6 +67,14 @@ class StepMetadata:
         self.decode.refill(self.cu_seqlens_q, self.seqlens_kv, causal_base)
         self._plan_prefill(causal_base)
         return self
+
+
+def cached_step_metadata(ctx, num_q_heads: int, num_kv_heads: int, head_dim: int, device):
+    """The metadata already attached to ``ctx`` for this head geometry, or None."""
+    cache = getattr(ctx, _ATTR, None)
+    if cache is None:
+        return None
+    return cache.get((num_q_heads, num_kv_heads, head_dim, str(device)))
 
 
 def step_metadata(ctx, num_q_heads: int, num_kv_heads: int, head_dim: int, device,

@@ -13,7 +13,7 @@ import torch
 
 from . import ops
 from .base import AttentionBackend
-from .gqa import rms_norm, rotate_half
+from .gqa import rms_norm
 
 
 def ds_rope_interleave(x: torch.Tensor) -> torch.Tensor:
@@ -34,13 +34,23 @@ def build_absorb_weights(kv_b_weight, num_heads, qk_nope, v_head_dim, kv_lora_ra
 class B200MlaBackend(AttentionBackend):
     """Constructor keywords follow ``MlaFIABackend`` (mla.py:190-211).  Only the
     absorbed form is built (``absorb`` must stay True): it is the one whose cache
-    is 9x smaller and whose attention is a single dense contraction."""
+    is 9x smaller and whose attention is a single dense contraction.  ``num_heads`` is
+    the number of heads THIS rank holds and may not exceed 16 (one 16-row MMA tile per
+    sequence): DeepSeek-V3's 128 heads run at a head-parallel degree of 8 or more."""
+
+    MAX_HEADS_PER_RANK = 16
 
     def __init__(self, w: dict, *, num_heads: int, qk_nope: int, qk_rope: int, v_head_dim: int,
                  kv_lora_rank: int, q_lora_rank, rms_eps: float, softmax_scale: float,
                  num_layers: int, device, dtype, absorb: bool = True, layer_prefix=None):
         if not absorb:
             raise NotImplementedError("the B200 MLA backend implements the absorbed latent form only")
+        if num_heads > self.MAX_HEADS_PER_RANK:
+            raise ValueError(
+                f"the latent decode kernel takes q_len * heads <= {self.MAX_HEADS_PER_RANK} rows per "
+                f"sequence; {num_heads} heads per rank need tensor parallelism of at least "
+                f"{(num_heads + self.MAX_HEADS_PER_RANK - 1) // self.MAX_HEADS_PER_RANK} "
+                "(MLA has no all-reduce inside attention, auto_infer/layers/attention/mla.py:282-285)")
         self.w = w
         self.num_heads = num_heads
         self.qk_nope = qk_nope
@@ -77,6 +87,11 @@ class B200MlaBackend(AttentionBackend):
         return self._absorb_w[layer_idx]
 
     def attention(self, layer_idx: int, x: torch.Tensor, ctx) -> torch.Tensor:
+        """The sub-block of ``mla_paged_absorbed`` (auto_infer/layers/attention/mla.py:76-122;
+        its wiring is the plug-in contract, so the steps and their names follow it): q
+        projection (optionally through the q-LoRA), kv_a projection, then ONE fused launch
+        for the latent RMSNorm, both interleaved rotary embeddings and the latent slot
+        write, the absorbed query, latent attention, W_UV, o_proj."""
         w, prefix = self.w, self.layer_prefix(layer_idx)
         t = x.shape[0]
         nh, nope, rope, vd, kvl = (self.num_heads, self.qk_nope, self.qk_rope, self.v_head_dim,
@@ -90,25 +105,28 @@ class B200MlaBackend(AttentionBackend):
         q = q.view(t, nh, nope + rope)
         q_nope, q_pe = q.split([nope, rope], dim=-1)
         ckv_full = x @ w[prefix + "self_attn.kv_a_proj_with_mqa.weight"].t()
-        ckv, k_pe = ckv_full.split([kvl, rope], dim=-1)
-        ckv = rms_norm(ckv, w[prefix + "self_attn.kv_a_layernorm.weight"], self.rms_eps)
-        k_pe = k_pe.view(t, 1, rope)
-        q_pe = ds_rope_interleave(q_pe)
-        k_pe = ds_rope_interleave(k_pe)
-        q_pe = q_pe * ctx.cos + rotate_half(q_pe) * ctx.sin
-        k_pe = k_pe * ctx.cos + rotate_half(k_pe) * ctx.sin
         w_uk, w_uv = self._weights(layer_idx)
-        q_latent = torch.cat([torch.einsum("tnp,npl->tnl", q_nope, w_uk), q_pe], dim=-1).contiguous()
-        k_latent = torch.cat([ckv.unsqueeze(1), k_pe], dim=-1).contiguous()
-        o_latent = self.latent_attention(layer_idx, q_latent, k_latent, ctx)
+        q_latent = torch.empty(t, nh, kvl + rope, dtype=x.dtype, device=x.device)
+        q_latent[..., :kvl] = torch.einsum("tnp,npl->tnl", q_nope, w_uk)
+        latent_cache = ctx.kv_caches[layer_idx][0]
+        ops.mla_rope_norm_cache(ckv_full, w[prefix + "self_attn.kv_a_layernorm.weight"], self.rms_eps, q_pe,
+                                q_latent[..., kvl:], ctx.cos, ctx.sin, latent_cache, ctx.slot_mapping,
+                                kv_lora_rank=kvl)
+        o_latent = self._latent_attn(layer_idx, q_latent, ctx)
         o = torch.einsum("tnl,nvl->tnv", o_latent, w_uv)
         return o.reshape(t, nh * vd) @ w[prefix + "self_attn.o_proj.weight"].t()
 
     # -- the accelerated part: latent write + latent attention --------------
     def latent_attention(self, layer_idx: int, q_latent: torch.Tensor, k_latent: torch.Tensor,
                          ctx) -> torch.Tensor:
+        """Latent slot write followed by latent attention for rows that are already normed and
+        rotated."""
         latent_cache = ctx.kv_caches[layer_idx][0]
         ops.reshape_and_cache(k_latent, None, latent_cache, None, ctx.slot_mapping)
+        return self._latent_attn(layer_idx, q_latent, ctx)
+
+    def _latent_attn(self, layer_idx: int, q_latent: torch.Tensor, ctx) -> torch.Tensor:
+        latent_cache = ctx.kv_caches[layer_idx][0]
         plan, block_table = self._plan(ctx, q_latent.device)
         return ops.mla_decode_absorbed(q_latent, latent_cache, block_table, plan,
                                        self.softmax_scale, kv_lora_rank=self.kv_lora_rank)

@@ -426,3 +426,127 @@ def cp_exchange_combine(local_record: torch.Tensor, recv_ptrs_dev: int, state: t
             status_word(local_record.device).data_ptr(), _stream_ptr(local_record.device))
     _lib.check(rc, "b200_cp_exchange_combine")
     return out
+
+
+def _cache_tensors(layer):
+    return layer if isinstance(layer, tuple) else (layer,)
+
+
+def copy_blocks(source_caches, target_caches, block_ids, target_block_ids=None) -> None:
+    """Copy selected physical blocks between caches with identical layouts; same contract as
+    ``copy_blocks`` of auto_infer/pd/connector.py:30-51 (a tensor cache is the dense
+    ``(2, blocks, ...)`` layout, a tuple holds separate key / value tensors whose leading
+    axis is the block axis), one kernel launch per cache tensor instead of one copy per
+    block.  ``target_block_ids`` (optional, beyond the reference) lands the pages on other
+    block ids of the target pool."""
+    if len(source_caches) != len(target_caches):
+        raise ValueError("source and target cache layer counts must match")
+    lib = _lib.load()
+    ids = torch.as_tensor(block_ids, dtype=torch.int32)
+    if ids.numel() == 0:
+        return
+    dst_ids = None
+    if target_block_ids is not None:
+        dst_ids = torch.as_tensor(target_block_ids, dtype=torch.int32)
+        if dst_ids.numel() != ids.numel():
+            raise ValueError("block_ids and target_block_ids must have the same length")
+    ids_dev = {}
+    for source_layer, target_layer in zip(source_caches, target_caches):
+        source_tensors = _cache_tensors(source_layer)
+        target_tensors = _cache_tensors(target_layer)
+        if len(source_tensors) != len(target_tensors):
+            raise ValueError("source and target cache layouts must match")
+        separate_kv = isinstance(source_layer, tuple)
+        for source, target in zip(source_tensors, target_tensors):
+            block_axis = 0 if separate_kv else 1
+            same = (source.shape == target.shape) if dst_ids is None else (
+                source.shape[:block_axis] + source.shape[block_axis + 1:] ==
+                target.shape[:block_axis] + target.shape[block_axis + 1:])
+            if not same:
+                raise ValueError("source and target cache shapes must match")
+            _need_cuda(source, target)
+            if not (source.is_contiguous() and target.is_contiguous()):
+                raise ValueError("caches must be contiguous")
+            # the dense layout is two stacked pools: K pages, then V pages
+            halves = [(source, target)] if separate_kv else [(source[0], target[0]), (source[1], target[1])]
+            dev = source.device
+            if dev not in ids_dev:
+                ids_dev[dev] = (ids.to(dev), dst_ids.to(dev) if dst_ids is not None else None)
+            src_ids, tgt_ids = ids_dev[dev]
+            for src, dst in halves:
+                page_bytes = src[0].numel() * src.element_size()
+                with _on_device(dev):
+                    rc = lib.b200_copy_blocks(
+                        src.data_ptr(), dst.data_ptr(), src_ids.data_ptr(),
+                        tgt_ids.data_ptr() if tgt_ids is not None else None, ids.numel(), page_bytes,
+                        src.shape[0], dst.shape[0], status_word(dev).data_ptr(), _stream_ptr(dev))
+                _lib.check(rc, "b200_copy_blocks")
+
+
+def gqa_rope_cache(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                   key_cache: torch.Tensor, value_cache: torch.Tensor, slot_mapping: torch.Tensor,
+                   q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
+                   eps: float = 1e-6, want_k: bool = False):
+    """Fused prologue of the GQA sub-block (auto_infer/layers/attention/gqa.py:40-47): optional
+    per-head RMSNorm of q / k, NeoX rotary embedding of q / k, slot write of k and v.
+    q / k / v are (T, H*, 128) views (of the packed projection, typically); returns the rotated
+    q (T, Hq, 128) and, with ``want_k``, the rotated k."""
+    _need_cuda(q, k, v, cos, sin, key_cache, value_cache, slot_mapping)
+    lib = _lib.load()
+    t, n_q, d = q.shape
+    n_kv = k.shape[1]
+    for name, x in (("q", q), ("k", k), ("v", v)):
+        if x.stride(2) != 1 or x.stride(1) != d:
+            raise ValueError(f"{name}: each token's heads must be contiguous")
+    if cos.stride(-1) != 1 or sin.stride(-1) != 1 or cos.stride(0) != sin.stride(0):
+        raise ValueError("cos / sin must be (T, 1, D) with contiguous rows and equal token strides")
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("KV caches must be contiguous (num_blocks, block_size, Hkv, D)")
+    if slot_mapping.dtype != torch.int32:
+        slot_mapping = slot_mapping.to(torch.int32)
+    q_out = torch.empty(t, n_q, d, dtype=q.dtype, device=q.device)
+    k_out = torch.empty(t, n_kv, d, dtype=k.dtype, device=k.device) if want_k else None
+    num_blocks, block_size = key_cache.shape[0], key_cache.shape[1]
+    with _on_device(q.device):
+        rc = lib.b200_gqa_rope_cache(
+            q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+            cos.data_ptr(), sin.data_ptr(), cos.stride(0),
+            q_norm_weight.data_ptr() if q_norm_weight is not None else None,
+            k_norm_weight.data_ptr() if k_norm_weight is not None else None, float(eps),
+            q_out.data_ptr(), q_out.stride(0), k_out.data_ptr() if k_out is not None else None,
+            key_cache.data_ptr(), value_cache.data_ptr(), slot_mapping.contiguous().data_ptr(),
+            t, n_q, n_kv, d, block_size, num_blocks, status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "b200_gqa_rope_cache")
+    return (q_out, k_out) if want_k else q_out
+
+
+def mla_rope_norm_cache(ckv_full: torch.Tensor, norm_weight: torch.Tensor, eps: float, q_pe: torch.Tensor,
+                        q_pe_out: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                        latent_cache: torch.Tensor, slot_mapping: torch.Tensor, kv_lora_rank: int = 512,
+                        want_k_latent: bool = False) -> Optional[torch.Tensor]:
+    """Fused prologue of the absorbed-MLA sub-block (auto_infer/layers/attention/mla.py:96-113):
+    latent RMSNorm, interleaved rotary embedding of the decoupled key and of every head's q_pe
+    (written to ``q_pe_out``, any (T, H, 64) view), slot write of the latent row."""
+    _need_cuda(ckv_full, norm_weight, q_pe, q_pe_out, cos, sin, latent_cache, slot_mapping)
+    lib = _lib.load()
+    t, width = ckv_full.shape
+    rope = width - kv_lora_rank
+    h = q_pe.shape[1]
+    if ckv_full.stride(1) != 1 or q_pe.stride(2) != 1 or q_pe_out.stride(2) != 1:
+        raise ValueError("rows must be contiguous along their last axis")
+    if not latent_cache.is_contiguous():
+        raise ValueError("latent cache must be contiguous (num_blocks, block_size, 1, kvl+rope)")
+    if slot_mapping.dtype != torch.int32:
+        slot_mapping = slot_mapping.to(torch.int32)
+    k_latent = torch.empty(t, 1, width, dtype=ckv_full.dtype, device=ckv_full.device) if want_k_latent else None
+    num_blocks, block_size = latent_cache.shape[0], latent_cache.shape[1]
+    with _on_device(ckv_full.device):
+        rc = lib.b200_mla_rope_norm_cache(
+            ckv_full.data_ptr(), ckv_full.stride(0), norm_weight.data_ptr(), float(eps),
+            q_pe.data_ptr(), q_pe.stride(0), q_pe.stride(1), q_pe_out.data_ptr(), q_pe_out.stride(0),
+            q_pe_out.stride(1), cos.data_ptr(), sin.data_ptr(), cos.stride(0), latent_cache.data_ptr(),
+            k_latent.data_ptr() if k_latent is not None else None, slot_mapping.contiguous().data_ptr(),
+            t, h, kv_lora_rank, rope, block_size, num_blocks, status_word(ckv_full.device).data_ptr(),
+            _stream_ptr(ckv_full.device))
+    _lib.check(rc, "b200_mla_rope_norm_cache")
+    return k_latent

@@ -38,22 +38,25 @@ def _dense_unavailable(family: str):
 
 
 def _gqa(model, mode: str):
-    from .gqa import B200GqaBackend
+    from .gqa import B200GqaBackend, B200GraphGqaBackend
     if mode == "dense":
         _dense_unavailable("gqa")
     cfg = model.cfg
-    # "graph" and "paged" are one backend here: sequence lengths are read from
-    # device memory, so a captured step needs no per-replay host re-issue.
-    return B200GqaBackend(
+    # "graph": the same kernels behind the lifecycle surface the graph runners drive
+    # (auto_infer/layers/attention/gqa.py:134-226); lengths are read from a refillable plan
+    # in device memory, so a replay needs one plan refill instead of a per-layer re-issue.
+    cls = B200GraphGqaBackend if mode == "graph" else B200GqaBackend
+    return cls(
         n_q_heads=model.n_q_local, n_kv_heads=model.n_kv_local, head_dim=cfg.head_dim,
         scale=cfg.head_dim ** -0.5, num_layers=cfg.num_layers, device=model.device,
         dtype=model.dtype, w=model.w, layer_prefix=model.layer_prefix, rms_eps=cfg.rms_eps)
 
 
 def _gqa_mtp(model, mode: str, prefix: str):
-    from .gqa import B200GqaBackend
+    from .gqa import B200GqaBackend, B200GraphGqaBackend
     cfg = model.cfg
-    return B200GqaBackend(
+    cls = B200GraphGqaBackend if mode == "graph" else B200GqaBackend
+    return cls(
         n_q_heads=model.n_q_local, n_kv_heads=model.n_kv_local, head_dim=cfg.head_dim,
         scale=cfg.head_dim ** -0.5, num_layers=1, device=model.device, dtype=model.dtype,
         w=model.w, layer_prefix=lambda _: prefix, rms_eps=cfg.rms_eps)

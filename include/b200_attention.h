@@ -322,6 +322,63 @@ int b200_cp_exchange_combine(const float* local_record, const uint64_t* recv_ptr
                              void* out, int out_is_f32, float* lse_out,
                              int32_t* status, void* stream);
 
+/* ------------------------------------------------------------------------ *
+ * Fused prologue of the GQA attention sub-block: what auto-infer runs between
+ * the QKV projection and the attention call as separate elementwise ops
+ * (auto_infer/layers/attention/gqa.py:40-47): optional per-head RMSNorm of q and
+ * k (Qwen3; layers/norm.py:5-9), NeoX rotary embedding of q and k
+ * (layers/rotary_embedding/__init__.py:10-12) and the slot write of k and v
+ * (base.py:41-45).
+ *   q / k / v: (T, H*, 128) bf16 views of the packed projection, token strides in
+ *     elements; cos / sin (T, 1, 128) bf16, token stride cos_sin_stride
+ *   q_norm_weight / k_norm_weight: (128) bf16, both or neither
+ *   q_out (T, Hq, 128) bf16 (token stride q_out_stride): the rotated queries
+ *   k_out (T, Hkv, 128) bf16 or NULL: the rotated keys, for callers that want them
+ *   caches / slot_mapping: as b200_reshape_and_cache
+ * Rounds to bf16 where the eager chain of bf16 tensors does, so q_out and the
+ * cache rows equal that chain's. */
+int b200_gqa_rope_cache(const void* q, int64_t q_stride, const void* k, int64_t k_stride,
+                        const void* v, int64_t v_stride,
+                        const void* cos, const void* sin, int64_t cos_sin_stride,
+                        const void* q_norm_weight, const void* k_norm_weight, float eps,
+                        void* q_out, int64_t q_out_stride, void* k_out,
+                        void* key_cache, void* value_cache, const int32_t* slot_mapping,
+                        int num_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                        int block_size, int num_blocks, int32_t* status, void* stream);
+
+/* Fused prologue of the absorbed-MLA sub-block (auto_infer/layers/attention/
+ * mla.py:96-113): RMSNorm of the 512-wide latent, interleaved-to-halves
+ * regrouping (layers/rotary_embedding/__init__.py:15-23) and rotary embedding
+ * of the 64-wide decoupled key and of every head's q_pe, and the slot write of
+ * the latent row [ckv | k_pe] into the single latent cache.
+ *   ckv_full (T, 576) bf16: output of kv_a_proj_with_mqa, token stride ckv_stride
+ *   q_pe (T, H, 64) bf16 view (token / head strides in elements) -> q_pe_out, a
+ *     view of the same shape (e.g. the last 64 columns of the q_latent buffer)
+ *   k_latent_out (T, 576) bf16 or NULL: the row as cached */
+int b200_mla_rope_norm_cache(const void* ckv_full, int64_t ckv_stride,
+                             const void* norm_weight, float eps,
+                             const void* q_pe, int64_t q_pe_stride_t, int64_t q_pe_stride_h,
+                             void* q_pe_out, int64_t q_out_stride_t, int64_t q_out_stride_h,
+                             const void* cos, const void* sin, int64_t cos_sin_stride,
+                             void* latent_cache, void* k_latent_out, const int32_t* slot_mapping,
+                             int num_tokens, int num_heads, int kv_lora_rank, int rope_dim,
+                             int block_size, int num_blocks, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Copy of selected pages between two paged caches of identical page layout (one
+ * K or V tensor per call): the prefill-to-decode block transfer of
+ * auto_infer/pd/connector.py:30-51 (copy_blocks), which copies block by block
+ * with one tensor copy each.  Page i of the list goes from block
+ * src_block_ids[i] of src_cache to block dst_block_ids[i] of dst_cache
+ * (dst_block_ids NULL = the same ids, the reference's form).  The two caches
+ * may sit on different GPUs of a node if one of them is peer-mapped into the
+ * current device.  page_bytes = block_size * Hkv * dim * 2 must be a multiple of
+ * 16.  Ids outside a pool are skipped and set B200_STATUS_BAD_BLOCK.  Bit-exact. */
+int b200_copy_blocks(const void* src_cache, void* dst_cache,
+                     const int32_t* src_block_ids, const int32_t* dst_block_ids, int num_ids,
+                     int64_t page_bytes, int num_src_blocks, int num_dst_blocks,
+                     int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

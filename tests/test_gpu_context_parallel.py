@@ -43,6 +43,37 @@ def test_emulated_ranks_merge_to_the_unsplit_answer(ranks):
     assert ops.read_status("cuda") == 0
 
 
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_emulated_ranks_with_prefill_chunks(ranks):
+    """Context-parallel chunked prefill: every rank runs the wide-query kernel over its own
+    slice of the keys (a chunk of 150 tokens over a 300-token prefix, a whole 200-token prompt,
+    beside a decode row) and the partials merge to the unsplit answer - where the reference's
+    context-parallel prefill gathers all K and V on every rank (auto_infer/models/qwen2.py:181-226).
+    Rows that see none of a rank's keys come out as an empty part."""
+    from auto_infer_b200 import context_parallel as cp, ops, synth
+    b = synth.build_gqa_batch("cp_prefill", [(150, 450), (1, 700), (200, 200)], 16, 4, 128, 24, 19)
+    ref, ref_lse = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                                       b.seqlens_kv, b.scale, return_lse=True)
+    d = b.to("cuda")
+    rows = b.num_tokens * b.n_q
+    gathered = torch.empty(ranks, rows * (b.head_dim + 1), dtype=torch.float32, device="cuda")
+    for r in range(ranks):
+        local_bt = cp.shard_block_table(d.block_table, b.seqlens_kv, 128, r, ranks)
+        step = cp.ContextParallelDecode(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, 128, "cuda",
+                                        cp_rank=r, cp_size=ranks)
+        assert step.meta.prefill is not None
+        step.partial.flat.fill_(float("nan"))
+        step._local(d.q, d.kv_cache[0], d.kv_cache[1], local_bt, b.scale, step.partial.o, step.partial.lse)
+        gathered[r].copy_(step.partial.flat)
+    assert torch.isfinite(gathered[:, : rows * b.head_dim]).all()
+    o_parts, lse_parts = cp.split_gathered(gathered, rows, b.head_dim)
+    lse = torch.empty(rows, dtype=torch.float32, device="cuda")
+    out = ops.lse_combine(o_parts, lse_parts, lse_out=lse)
+    assert_attention_close(out.view_as(ref).cpu(), ref, lse.view_as(ref_lse).cpu(), ref_lse,
+                           f"{ranks} emulated ranks, prefill chunks")
+    assert ops.read_status("cuda") == 0
+
+
 def test_exchange_wait_for_an_absent_peer_runs_out_and_the_next_step_works():
     """The fused exchange waits for its peers with a limit.  Two 'ranks' share this GPU, each
     with its own receive buffer and step counter, and run one after the other, so the first
@@ -95,7 +126,7 @@ def _nccl_worker(rank, world, port, ret, use_p2p=False):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
-        b = synth.build_gqa_batch("cp", [(1, 3000), (2, 700), (1, 130)], 16, 8, 128, 40, 23)
+        b = synth.build_gqa_batch("cp", [(1, 3000), (2, 700), (1, 130), (70, 400)], 16, 8, 128, 40, 23)
         d = b.to(f"cuda:{rank}")
         local_bt = cp.shard_block_table(d.block_table, b.seqlens_kv, 128, rank, world)
         exchange = cp.PeerExchange(b.num_tokens * b.n_q, b.head_dim, f"cuda:{rank}") if use_p2p else None

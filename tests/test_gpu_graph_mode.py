@@ -1,0 +1,128 @@
+"""Graph mode on the GPU: ONE decode step is recorded into a CUDA graph and replayed for
+other length sets without recapture, the way the reference's graph runners drive a gear
+(auto_infer/worker/graph_decode_runner.py ``_capture`` / ``_prepare_graph``): static
+per-gear buffers staged in place, padding rows on scratch blocks with kv_len 1
+(auto_infer/worker/decode_input_stager.py:74-123), ``backend.update(ctx)`` with the step's
+lengths, ``graph.replay()``.  Every replay must equal the oracle."""
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+from oracle import paged_attention_oracle as orc
+from tests.parity import assert_attention_close
+
+pytestmark = pytest.mark.gpu
+
+BS, GEAR, MAX_BLOCKS, NUM_BLOCKS, N_Q, N_KV, HD = 16, 4, 24, 64, 8, 2, 128
+SCRATCH0 = NUM_BLOCKS                      # scratch blocks sit on top of the pool the engine hands out
+
+
+def _stage(requests):
+    """The reference stager's arithmetic for a decode gear: live rows first, then padding rows
+    on their own scratch block.  requests: (position of the new token, block ids)."""
+    slots, kv_lens = [], []
+    bt = torch.zeros(GEAR, MAX_BLOCKS, dtype=torch.int32)
+    for row, (pos, blocks) in enumerate(requests):
+        slots.append(blocks[pos // BS] * BS + pos % BS)
+        bt[row, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+        kv_lens.append(pos + 1)
+    for row in range(len(requests), GEAR):
+        block = SCRATCH0 + row
+        slots.append(block * BS)
+        bt[row, 0] = block
+        kv_lens.append(1)
+    return torch.tensor(slots, dtype=torch.int32), bt, kv_lens
+
+
+def test_one_captured_decode_step_replays_for_other_lengths():
+    from auto_infer_b200 import ops, registry
+    from auto_infer_b200.forward_context import ForwardContext
+    from auto_infer_b200.gqa import B200GraphGqaBackend
+    dev = torch.device("cuda")
+    cfg = SimpleNamespace(head_dim=HD, num_layers=2, rms_eps=1e-6)
+    model = SimpleNamespace(cfg=cfg, n_q_local=N_Q, n_kv_local=N_KV, w={}, layer_prefix=lambda i: f"model.layers.{i}.",
+                            device=dev, dtype=torch.bfloat16, ATTENTION_FAMILY="gqa")
+    backend, caches = registry.build_attention_backend(model, "graph", NUM_BLOCKS + GEAR, BS)
+    assert isinstance(backend, B200GraphGqaBackend)
+    g = torch.Generator().manual_seed(2024)
+    for kc, vc in caches:                                   # a cache with history in every block
+        kc.copy_(torch.randn(kc.shape, generator=g).to(torch.bfloat16))
+        vc.copy_(torch.randn(vc.shape, generator=g).to(torch.bfloat16))
+
+    # the gear's static buffers (what a captured graph is recorded against)
+    q = torch.zeros(GEAR, N_Q, HD, dtype=torch.bfloat16, device=dev)
+    k_new = torch.zeros(GEAR, N_KV, HD, dtype=torch.bfloat16, device=dev)
+    v_new = torch.zeros(GEAR, N_KV, HD, dtype=torch.bfloat16, device=dev)
+    slots = torch.zeros(GEAR, dtype=torch.int32, device=dev)
+    block_table = torch.zeros(GEAR, MAX_BLOCKS, dtype=torch.int32, device=dev)
+    cu_q = list(range(1, GEAR + 1))
+
+    def ctx_for(kv_lens):
+        return ForwardContext(None, None, slots, block_table, cu_q, kv_lens, None, backend, caches, True)
+
+    def step(ctx):
+        return [backend.paged_attention(layer, q, k_new, v_new, ctx) for layer in range(cfg.num_layers)]
+
+    # capture on scratch rows only, as the reference does (kv_len 1 everywhere)
+    s0, bt0, kv0 = _stage([])
+    slots.copy_(s0)
+    block_table.copy_(bt0)
+    ctx = ctx_for(kv0)
+    backend.capturing = False
+    step(ctx)                                               # warm-up: plan buffers come to life here
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    backend.begin_capture()
+    with torch.cuda.graph(graph):
+        outs = step(ctx)
+    backend.end_capture()
+    gear_reg = backend.reg
+    assert len(gear_reg) == cfg.num_layers and gear_reg[0].meta is gear_reg[1].meta
+
+    perm = torch.randperm(NUM_BLOCKS, generator=g).tolist()
+    length_sets = [
+        [(5, perm[0:1]), (17, perm[1:3])],                                     # two live rows, two padding rows
+        [(0, perm[3:4]), (300, perm[4:23]), (63, perm[23:27]), (16, perm[27:29])],   # full gear, long and short
+        [(BS * MAX_BLOCKS - 1, perm[29:29 + MAX_BLOCKS])],                     # one row at the longest length
+    ]
+    for requests in length_sets:
+        s_h, bt_h, kv_lens = _stage(requests)
+        q_h = torch.randn(GEAR, N_Q, HD, generator=g).to(torch.bfloat16)
+        k_h = torch.randn(GEAR, N_KV, HD, generator=g).to(torch.bfloat16)
+        v_h = torch.randn(GEAR, N_KV, HD, generator=g).to(torch.bfloat16)
+        for dst, src in ((q, q_h), (k_new, k_h), (v_new, v_h), (slots, s_h), (block_table, bt_h)):
+            dst.copy_(src)
+        # an eager step of another shape in between must not disturb the captured plan
+        other = ForwardContext(None, None, slots[:1], block_table[:1], [1], [kv_lens[0]], None, backend, caches, True)
+        ref_caches = [(kc.cpu().clone(), vc.cpu().clone()) for kc, vc in caches]
+        backend.paged_attention(0, q[:1], k_new[:1], v_new[:1], other)
+        backend.update_registrations(gear_reg, ctx_for(kv_lens))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        live = len(requests)
+        for layer in range(cfg.num_layers):
+            kc, vc = ref_caches[layer]
+            orc.write_kv(k_h, v_h, kc, vc, s_h.tolist())
+            assert torch.equal(caches[layer][0].cpu(), kc) and torch.equal(caches[layer][1].cpu(), vc)
+            ref, _ = orc.paged_attention(q_h, kc, vc, bt_h, cu_q, kv_lens, HD ** -0.5, return_lse=True)
+            got = outs[layer].cpu()
+            assert_attention_close(got[:live], ref[:live], what=f"layer {layer}, lengths {kv_lens}")
+            assert torch.isfinite(got.float()).all()                          # padding rows: discarded, but sane
+            assert_attention_close(got[live:], ref[live:], what="padding rows")
+
+
+def test_capture_without_a_warm_up_step_is_refused():
+    from auto_infer_b200.forward_context import ForwardContext
+    from auto_infer_b200.gqa import B200GraphGqaBackend
+    dev = torch.device("cuda")
+    backend = B200GraphGqaBackend(N_Q, N_KV, HD, HD ** -0.5, 1, dev, torch.bfloat16)
+    caches = backend.alloc_kv_caches(8, BS)
+    q = torch.zeros(1, N_Q, HD, dtype=torch.bfloat16, device=dev)
+    ctx = ForwardContext(None, None, torch.zeros(1, dtype=torch.int32, device=dev),
+                         torch.zeros(1, 4, dtype=torch.int32, device=dev), [1], [1], None, backend, caches, True)
+    backend.begin_capture()
+    with pytest.raises(RuntimeError, match="one eager step with the same context first"):
+        backend._attn(0, q, None, None, ctx)
+    backend.end_capture()

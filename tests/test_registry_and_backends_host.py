@@ -35,13 +35,35 @@ def test_backend_interface_is_abstract_and_minimal():
 
 
 def test_gqa_family_builds_paged_and_graph_backends_with_reference_cache_shape():
-    for mode in ("paged", "graph"):
-        backend, caches = registry.build_attention_backend(_gqa_model(), mode, num_blocks=5, block_size=128)
-        assert isinstance(backend, B200GqaBackend)
-        assert len(caches) == 3
-        assert caches[0].shape == (2, 5, 128, 2, 128) and caches[0].dtype == torch.bfloat16
-        assert float(caches[0].abs().sum()) == 0.0
-        assert backend.scale == 128 ** -0.5
+    backend, caches = registry.build_attention_backend(_gqa_model(), "paged", num_blocks=5, block_size=128)
+    assert isinstance(backend, B200GqaBackend)
+    assert len(caches) == 3
+    assert caches[0].shape == (2, 5, 128, 2, 128) and caches[0].dtype == torch.bfloat16
+    assert float(caches[0].abs().sum()) == 0.0
+    assert backend.scale == 128 ** -0.5
+
+
+def test_graph_mode_has_the_lifecycle_surface_the_graph_runners_drive():
+    """Attributes read by auto_infer/worker/graph_decode_runner.py:231,281,389-400,432-449
+    and the two-tensor cache of auto_infer/layers/attention/gqa.py:192-200."""
+    from auto_infer_b200.gqa import B200GraphGqaBackend
+    backend, caches = registry.build_attention_backend(_gqa_model(), "graph", num_blocks=5, block_size=16)
+    assert isinstance(backend, B200GraphGqaBackend) and isinstance(backend, B200GqaBackend)
+    assert len(caches) == 3 and len(caches[0]) == 2
+    assert caches[0][0].shape == caches[0][1].shape == (5, 16, 2, 128)
+    assert caches[0][0].data_ptr() != caches[0][1].data_ptr()
+    assert backend.capturing is False and backend.reg == []
+    assert backend.supports_prefill_graph is False
+    backend.begin_capture()
+    assert backend.capturing is True and backend.reg == []
+    backend.end_capture()
+    assert backend.capturing is False
+    for name in ("update", "update_registrations", "update_many"):
+        assert callable(getattr(backend, name))
+    with pytest.raises(ValueError, match="graph-task contexts must match registrations"):
+        backend.update_many([object()])
+    mtp, _ = registry.build_mtp_attention_backend(_gqa_model(), "graph", "model.mtp_layers.0.", 2, 16)
+    assert isinstance(mtp, B200GraphGqaBackend) and mtp.num_layers == 1
 
 
 def test_mla_family_caches_the_latent_once():
@@ -160,7 +182,7 @@ def test_install_into_auto_infer_serves_the_reference_builders():
     assert isinstance(backend, B200GqaBackend)
     assert len(caches) == 3 and caches[0].shape == (2, 3, 128, 2, 128)
     backend, caches = ref.build_attention_backend(_gqa_model("gqa_b200"), "graph", num_blocks=3, block_size=128)
-    assert isinstance(backend, B200GqaBackend)
+    assert isinstance(backend, B200GqaBackend) and hasattr(backend, "update_many") and len(caches[0]) == 2
 
     from auto_infer.layers.attention.gqa import DenseBackend
     from auto_infer.layers.attention.mla import MlaDenseBackend
@@ -179,3 +201,15 @@ def test_install_into_auto_infer_serves_the_reference_builders():
     assert mtp.layer_prefix(0) == "model.mtp_layers.0." and len(caches) == 1
     with pytest.raises(ValueError, match="unsupported MTP attention mode"):
         ref.build_mtp_attention_backend(_gqa_model("gqa_b200"), "dense", "model.mtp_layers.0.")
+
+
+def test_mla_backend_refuses_more_heads_than_the_kernel_holds():
+    """128 heads on one rank (DeepSeek-V3 without head parallelism) must fail at construction
+    with the reason, not on the first step."""
+    with pytest.raises(ValueError, match="tensor parallelism of at least 8"):
+        B200MlaBackend({}, num_heads=128, qk_nope=128, qk_rope=64, v_head_dim=128, kv_lora_rank=512,
+                       q_lora_rank=None, rms_eps=1e-6, softmax_scale=192 ** -0.5, num_layers=1,
+                       device="cpu", dtype=torch.bfloat16)
+    B200MlaBackend({}, num_heads=16, qk_nope=128, qk_rope=64, v_head_dim=128, kv_lora_rank=512,
+                   q_lora_rank=None, rms_eps=1e-6, softmax_scale=192 ** -0.5, num_layers=1,
+                   device="cpu", dtype=torch.bfloat16)
