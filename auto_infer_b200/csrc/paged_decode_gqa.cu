@@ -501,10 +501,8 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     if (qlane == 0) {
       sm.red_m[warp][quad] = m0;
       sm.red_m[warp][quad + 8] = m1;
-      sm.red_l[warp][quad] = l0;
-      sm.red_l[warp][quad + 8] = l1;
     }
-    named_bar_sync(1, kConsumerThreads);                       // (1) every warp's m and l are in place
+    named_bar_sync(1, kConsumerThreads);                       // (1) every warp's row maxima are in place
 #ifdef B200_TRACE_PHASES
     if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 10] = (long long)global_timer_ns();
 #endif
@@ -513,6 +511,8 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       pending_multi = -1;
     }
     {
+      // bring this warp's sums and accumulators to the rows' common maximum; the scaled
+      // sums go to red_l, so that the row total later is eight loads and adds
       float g0 = -INFINITY, g1 = -INFINITY;
 #pragma unroll
       for (int ww = 0; ww < kConsumerWarps; ++ww) {
@@ -521,6 +521,10 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       }
       const float f0 = (m0 == -INFINITY) ? 0.f : fast_exp2((m0 - g0) * p.scale_log2);
       const float f1 = (m1 == -INFINITY) ? 0.f : fast_exp2((m1 - g1) * p.scale_log2);
+      if (qlane == 0) {
+        sm.red_l[warp][quad] = l0 * f0;
+        sm.red_l[warp][quad + 8] = l1 * f1;
+      }
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
         o[n][0] *= f0; o[n][1] *= f0; o[n][2] *= f1; o[n][3] *= f1;
@@ -530,38 +534,48 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     // warp stores at once would all land in the same banks.  Column groups of 8 floats are
     // XOR-ed with the row number (mod 4), which spreads them over all banks.
     const int swz = (quad & 3) << 3;              // same for row quad and row quad + 8
-    auto store_slot = [&](float* slot) {
+    if (warp >= 4) {
+      float* slot = sm.slots[warp - 4];
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
         const int col = (n * 8 + qlane * 2) ^ swz;
         *reinterpret_cast<float2*>(slot + quad * kHeadDim + col) = make_float2(o[n][0], o[n][1]);
         *reinterpret_cast<float2*>(slot + (quad + 8) * kHeadDim + col) = make_float2(o[n][2], o[n][3]);
       }
-    };
-    if (warp >= 4) store_slot(sm.slots[warp - 4]);
-    named_bar_sync(1, kConsumerThreads);                       // (2)
+    }
+    named_bar_sync(1, kConsumerThreads);                       // (2) warps 4-7 have parked their sums
 #ifdef B200_TRACE_PHASES
     if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 11] = (long long)global_timer_ns();
 #endif
     if (warp < 4) {
-      const float* slot = sm.slots[warp];
+      // Add the partner warp's sums in place: a thread rewrites exactly the words it read.  The
+      // loads of four column groups are issued together before any of their stores: written as
+      // load-add-store per word, every load would wait behind the store before it (the compiler
+      // must assume they alias) and the warp would pay one shared-memory latency per word.
+      float* slot = sm.slots[warp];
 #pragma unroll
-      for (int n = 0; n < 16; ++n) {
-        const int col = (n * 8 + qlane * 2) ^ swz;
-        const float2 a = *reinterpret_cast<const float2*>(slot + quad * kHeadDim + col);
-        const float2 b = *reinterpret_cast<const float2*>(slot + (quad + 8) * kHeadDim + col);
-        o[n][0] += a.x; o[n][1] += a.y; o[n][2] += b.x; o[n][3] += b.y;
+      for (int n0 = 0; n0 < 16; n0 += 4) {
+        float2 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int col = ((n0 + u) * 8 + qlane * 2) ^ swz;
+          a[u] = *reinterpret_cast<const float2*>(slot + quad * kHeadDim + col);
+          b[u] = *reinterpret_cast<const float2*>(slot + (quad + 8) * kHeadDim + col);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int col = ((n0 + u) * 8 + qlane * 2) ^ swz;
+          *reinterpret_cast<float2*>(slot + quad * kHeadDim + col) =
+              make_float2(a[u].x + o[n0 + u][0], a[u].y + o[n0 + u][1]);
+          *reinterpret_cast<float2*>(slot + (quad + 8) * kHeadDim + col) =
+              make_float2(b[u].x + o[n0 + u][2], b[u].y + o[n0 + u][3]);
+        }
       }
     }
-    named_bar_sync(1, kConsumerThreads);                       // (3)
-#ifdef B200_TRACE_PHASES
-    if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 12] = (long long)global_timer_ns();
-#endif
-    if (warp < 4) store_slot(sm.slots[warp]);
     // 256 threads: thread -> rows (t / 32) and (t / 32 + 8), 4 columns each, so a warp reads and
-    // writes whole rows.  The rows' maxima and sums are taken from red_m / red_l BEFORE
-    // barrier (4): no warp writes those arrays again (next item) until every thread has
-    // passed (4), i.e. has finished reading them.
+    // writes whole rows.  The rows' maxima and scaled sums are taken from red_m / red_l
+    // BEFORE barrier (3): no warp writes those arrays again (next item) until every thread
+    // has passed (3), i.e. has finished reading them.
     const int t = threadIdx.x;
     const int col = (t & 31) * 4;
     float inv_r[2], lse_r[2];
@@ -569,19 +583,15 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     for (int h = 0; h < 2; ++h) {
       const int row = (t >> 5) + h * 8;
       float g = -INFINITY, lsum = 0.f;
-      if (row < rows) {
 #pragma unroll
-        for (int ww = 0; ww < kConsumerWarps; ++ww) g = fmaxf(g, sm.red_m[ww][row]);
-#pragma unroll
-        for (int ww = 0; ww < kConsumerWarps; ++ww) {
-          const float mw = sm.red_m[ww][row];
-          lsum += (mw == -INFINITY) ? 0.f : sm.red_l[ww][row] * fast_exp2((mw - g) * p.scale_log2);
-        }
+      for (int ww = 0; ww < kConsumerWarps; ++ww) {
+        g = fmaxf(g, sm.red_m[ww][row]);
+        lsum += sm.red_l[ww][row];
       }
       inv_r[h] = lsum > 0.f ? 1.f / lsum : 0.f;
       lse_r[h] = lsum > 0.f ? g * p.scale + __logf(lsum) : -INFINITY;
     }
-    named_bar_sync(1, kConsumerThreads);                       // (4) the four slots hold the warp-pair sums
+    named_bar_sync(1, kConsumerThreads);                       // (3) the four slots hold the warp-pair sums
 #ifdef B200_TRACE_PHASES
     if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 13] = (long long)global_timer_ns();
 #endif
@@ -628,8 +638,8 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
 #ifdef B200_TRACE
     if (p.trace && threadIdx.x == 0) p.trace[blockIdx.x * 16 + 5] = (long long)global_timer_ns();   // item written
 #endif
-    // The next item's first write to red_m / red_l comes after barrier (4) above, and its first
-    // write to the slots after its own barrier (1), which no thread passes before it has
+    // The next item's first write to red_m comes after barrier (3) above, and its first write to
+    // red_l and to the slots after its own barrier (1), which no thread passes before it has
     // finished the reads of this item.
   }
 

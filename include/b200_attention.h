@@ -300,17 +300,19 @@ int b200_lse_combine(const float* o_parts, const float* lse_parts,
  * reference, whose only CP code all-gathers K and V per layer,
  * auto_infer/models/qwen2.py:211-212).  Every rank pushes its packed fp32
  * record [o (rows*D) | lse (rows)] into the receive buffers of all ranks with
- * peer-to-peer stores, raises flags there, waits for the flags of all ranks in
- * its own buffer and merges the records from its own memory.  The rows are
- * dealt to the blocks of the grid; a block waits only for the same block of the
- * peers.
+ * peer-to-peer stores and merges the records that arrive in its own buffer.
+ * The records travel as flagged 16-byte lines {payload, step, payload, step}
+ * (two bf16 values of o per payload word, the row's lse as fp32 in a line of its
+ * own): a receiver polls the lines it is about to merge, so no separate flag and
+ * no acknowledgement round trip is needed.  The rows are dealt to the blocks of
+ * the grid; a block waits only for the lines of its own rows.
  *   recv_ptrs_dev: device array of `world` pointers, entry r = base of rank r's
  *     receive buffer as mapped in this process (symmetric memory; the caller
  *     sets it up, zero-filled, b200_cp_exchange_buffer_bytes() bytes per rank)
  *   state_dev: 4 uint32 of local device memory, zero-filled once
  *   wait_limit_ns: how long a block waits for a peer's flag; 0 = one second.
- *     When it runs out the block sets B200_STATUS_WAIT_TIMEOUT and leaves its
- *     rows of `out` unwritten; the step number still advances, so the next call
+ *     When it runs out the block sets B200_STATUS_WAIT_TIMEOUT and leaves the
+ *     rows it has not merged yet unwritten; the step number still advances, so the next call
  *     starts a fresh step.  Ranks should therefore be lined up (a host barrier
  *     after set-up) before the first exchange.
  * All ranks must call it once per step with the same shapes. */

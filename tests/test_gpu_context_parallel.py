@@ -114,7 +114,8 @@ def test_exchange_wait_for_an_absent_peer_runs_out_and_the_next_step_works():
         call(second, recs[second][0], out_second)
         torch.cuda.synchronize()
         assert ops.read_status("cuda") == 0
-        torch.testing.assert_close(out_second.cpu(), want, atol=1e-5, rtol=1e-5)
+        # the partial rows cross the link as bf16 (their log-sum-exp as fp32)
+        torch.testing.assert_close(out_second.cpu(), want, atol=2e-2, rtol=2e-2)
     assert [int(s[0]) for s in states] == [2, 2]                              # both ranks are at step 2
 
 
