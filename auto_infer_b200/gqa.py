@@ -14,12 +14,6 @@ from .base import AttentionBackend, _lin
 from .metadata import StepMetadata, cached_step_metadata, step_metadata
 
 
-def rotate_half(x: torch.Tensor) -> torch.Tensor:
-    """NeoX rotation (auto_infer/layers/rotary_embedding/__init__.py:10-12)."""
-    x1, x2 = x.chunk(2, dim=-1)
-    return torch.cat((-x2, x1), dim=-1)
-
-
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """RMSNorm over the last axis in fp32 (device-agnostic stand-in for the
     vendor op behind auto_infer/layers/norm.py:5-9)."""

@@ -16,13 +16,6 @@ from .base import AttentionBackend
 from .gqa import rms_norm
 
 
-def ds_rope_interleave(x: torch.Tensor) -> torch.Tensor:
-    """DeepSeek stores the rotary dims interleaved; regroup them into halves
-    before the NeoX rotation (auto_infer/layers/rotary_embedding/__init__.py:15-23)."""
-    d = x.shape[-1]
-    return x.view(*x.shape[:-1], d // 2, 2).transpose(-1, -2).reshape(*x.shape[:-1], d)
-
-
 def build_absorb_weights(kv_b_weight, num_heads, qk_nope, v_head_dim, kv_lora_rank):
     """kv_b_proj (H*(nope+vd), kvl) -> W_UK (H, nope, kvl), W_UV (H, vd, kvl)
     (auto_infer/layers/attention/mla.py:67-73)."""

@@ -163,13 +163,12 @@ class DecodePlan:
         self.num_seqs = len(cu_seqlens_q)
         if self.num_seqs > self.capacity_seqs:
             raise ValueError(f"{self.num_seqs} sequences exceed the plan's capacity of {self.capacity_seqs}")
-        cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
-        kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
-        base_ptr = None
-        if causal_base is not None:
-            base = torch.tensor(list(causal_base), dtype=torch.int32)
-            base_ptr = base.data_ptr()
-        rc = lib.b200_decode_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, self.num_seqs,
+        # plain C arrays: cheaper than tensors for a few dozen integers on the per-step path
+        int_array = ctypes.c_int32 * self.num_seqs
+        cu = int_array(*cu_seqlens_q)
+        kv = int_array(*seqlens_kv)
+        base = int_array(*causal_base) if causal_base is not None else None
+        rc = lib.b200_decode_plan(cu, kv, base, self.num_seqs,
                                   self.num_q_heads, self.num_kv_heads, self.num_ctas,
                                   self.host.data_ptr(), self._nbytes, ctypes.byref(self.info))
         _lib.check(rc, "b200_decode_plan")

@@ -388,14 +388,45 @@ def profile_case(args):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     batch = args.batch or 1
     if args.case == "merges":
-        # the two stand-alone merge kernels on config-5-sized records (8 ranks x 512 rows x 128)
+        # the small stand-alone kernels on config-5-sized operands: merge of 8 ranks' records
+        # (512 rows x 128), the fused exchange with one rank (push to and merge from this GPU's own
+        # buffer), the prologue kernels, the page copy
+        from auto_infer_b200 import _lib
         g = torch.Generator(device=dev).manual_seed(1)
         o = torch.randn(8, 512, 128, generator=g, device=dev)
         lse = torch.randn(8, 512, generator=g, device=dev)
-        name = "lse_combine on 8 x 512 x 128 records"
+        rec = torch.cat([o[0].reshape(-1), lse[0]]).contiguous()
+        nfloats = _lib.load().b200_cp_exchange_buffer_bytes(1, 512, 128) // 4
+        xbuf = torch.zeros(nfloats, dtype=torch.float32, device=dev)
+        xptr = torch.tensor([xbuf.data_ptr()], dtype=torch.int64, device=dev)
+        xstate = torch.zeros(4, dtype=torch.int32, device=dev)
+        xout = torch.empty(512, 128, dtype=torch.bfloat16, device=dev)
+        t, n_q, n_kv = 2048, 32, 8
+        qkv = torch.randn(t, (n_q + 2 * n_kv) * 128, generator=g, device=dev).to(torch.bfloat16)
+        q, k, v = qkv.split((n_q * 128, n_kv * 128, n_kv * 128), dim=-1)
+        cos = torch.randn(t, 1, 128, generator=g, device=dev).to(torch.bfloat16)
+        sin = torch.randn(t, 1, 128, generator=g, device=dev).to(torch.bfloat16)
+        nw = torch.ones(128, dtype=torch.bfloat16, device=dev)
+        cache = torch.zeros(2, 512, 128, n_kv, 128, dtype=torch.bfloat16, device=dev)
+        cache2 = torch.zeros_like(cache)
+        slots = torch.randperm(512 * 128, generator=g, device=dev)[:t].to(torch.int32)
+        ckv = torch.randn(t, 576, generator=g, device=dev).to(torch.bfloat16)
+        qm = torch.randn(t, 16, 192, generator=g, device=dev).to(torch.bfloat16)
+        ql = torch.empty(t, 16, 576, dtype=torch.bfloat16, device=dev)
+        lat = torch.zeros(512, 128, 1, 576, dtype=torch.bfloat16, device=dev)
+        cs64 = cos[..., :64].contiguous()
+        sn64 = sin[..., :64].contiguous()
+        ids = torch.randperm(512, generator=g, device=dev)[:256].tolist()
+        name = "lse_combine, cp_exchange (1 rank), rope/cache prologues, copy_blocks"
 
         def step():
             ops.lse_combine(o, lse)
+            ops.cp_exchange_combine(rec, xptr.data_ptr(), xstate, 0, 1, 512, 128, xout)
+            ops.gqa_rope_cache(q.view(t, n_q, 128), k.view(t, n_kv, 128), v.view(t, n_kv, 128), cos, sin,
+                               cache[0], cache[1], slots, q_norm_weight=nw, k_norm_weight=nw)
+            ops.mla_rope_norm_cache(ckv, torch.ones(512, dtype=torch.bfloat16, device=dev), 1e-6, qm[..., 128:],
+                                    ql[..., 512:], cs64, sn64, lat, slots)
+            ops.copy_blocks([cache], [cache2], ids)
     elif args.case == "c3":
         b = synth.config3(batch if args.batch else 64, dev)
         name = b.name

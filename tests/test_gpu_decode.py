@@ -164,3 +164,25 @@ def test_out_of_pool_block_id_is_flagged_not_fatal():
     torch.cuda.synchronize()
     assert ops.read_status("cuda") & 2
     assert torch.isfinite(out.float()).all()
+
+
+def test_unwritten_cache_slots_may_hold_anything():
+    """Slots of a sequence's last page past kv_len are never written by the engine: with NaN / Inf
+    bit patterns there (a pool from torch.empty), the rows must still come out finite and right -
+    their weight is 0, but 0 x NaN would poison the row if the bytes reached the MMA."""
+    from auto_infer_b200 import ops, synth
+    seqs = [(1, 70), (2, 129), (1, 64), (1, 5)]
+    b = synth.build_gqa_batch("poison", seqs, 8, 2, 128, 8, 314)
+    ref, ref_lse = orc.paged_attention(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, b.cu_seqlens_q,
+                                       b.seqlens_kv, b.scale, return_lse=True)
+    cache = b.kv_cache.clone()
+    for row, (_, kv_len) in zip(b.block_table.tolist(), seqs):
+        last = (kv_len - 1) // 128
+        tail = kv_len - last * 128
+        cache[0, row[last], tail:] = float("nan")
+        cache[1, row[last], tail:] = float("nan")
+        cache[1, row[last], tail::2] = float("inf")
+    out, lse = _decode(b.q, cache[0], cache[1], b.block_table, b.cu_seqlens_q, b.seqlens_kv, b.scale,
+                       b.n_q, b.n_kv, want_lse=True)
+    assert torch.isfinite(out.float()).all()
+    assert_attention_close(out, ref, lse, ref_lse, "poisoned tails")
