@@ -417,12 +417,12 @@ def cp_exchange_combine(local_record: torch.Tensor, recv_ptrs_dev: int, state: t
     ``wait_limit_ns`` bounds the wait for a peer (0 = one second)."""
     _need_cuda(local_record, state, out)
     lib = _lib.load()
-    with _on_device(local_record.device):
+    with _on_device(out.device):
         rc = lib.b200_cp_exchange_combine(
             local_record.data_ptr(), recv_ptrs_dev, state.data_ptr(), rank, world, rows, head_dim,
             int(wait_limit_ns), out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
             lse_out.data_ptr() if lse_out is not None else None,
-            status_word(local_record.device).data_ptr(), _stream_ptr(local_record.device))
+            status_word(out.device).data_ptr(), _stream_ptr(out.device))
     _lib.check(rc, "b200_cp_exchange_combine")
     return out
 
