@@ -62,6 +62,10 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, POINTER(PrefillPlanInfo), c_int, c_int, c_int, c_float,
         c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_paged_prefill_gqa_replayable": (c_int, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+        c_void_p, c_int, c_int, c_int, c_int, c_float,
+        c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_mla_decode_plan": (c_int, [
         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
         c_void_p, c_size_t, POINTER(DecodePlanInfo)]),

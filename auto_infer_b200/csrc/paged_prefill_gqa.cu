@@ -48,7 +48,7 @@ struct PrefillParams {
   int64_t bt_stride;
   const PrefillItem* items;
   int* work_counter;                // two plan words: next item to hand out, CTAs that have left
-  int num_items;
+                                    // (the word before them is the number of items)
   void* out;
   float* lse_out;
   int32_t* status;
@@ -213,7 +213,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
     const int4 lo = src[0], hi = src[1];
     rec = PrefillItem{lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
     mbar_arrive(&sm.item_empty[k & 1u]);
-    return (*abort_flag || idx < 0 || idx >= p.num_items) ? -1 : idx;
+    return (*abort_flag || idx < 0) ? -1 : idx;      // the producer has mapped an index past the list to -1
   };
 
   if (warp >= 8 && warp < 12) {
@@ -233,7 +233,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         // the first item of a CTA is its own index (no round trip to the counter before
         // the first load); the rest of the list is handed out dynamically
         idx = (k == 0) ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.work_counter, 1);
-        if (idx >= p.num_items || *abort_flag) idx = -1;
+        // the item count lives in the plan, not in the launch: a recorded launch serves other steps
+        if (idx >= __ldg(p.work_counter - 1) || *abort_flag) idx = -1;
         mbar_wait_bounded(&sm.item_empty[k & 1u], ((k >> 1) & 1u) ^ 1u, abort_flag, p.status);
         if (idx >= 0) {
           const int4* src = reinterpret_cast<const int4*>(p.items + idx);
@@ -736,34 +737,31 @@ static long long* g_pf_trace = nullptr;
 extern "C" void b200_debug_set_pf_trace(void* dev_ptr) { g_pf_trace = static_cast<long long*>(dev_ptr); }
 #endif
 
-extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const void* key_cache,
-                                      const void* value_cache, int num_blocks, int block_size,
-                                      const int32_t* block_table, int64_t bt_stride,
-                                      int32_t* plan_dev, const b200_prefill_plan_info* info,
-                                      int num_q_heads, int num_kv_heads, int head_dim, float scale,
-                                      void* out, int out_is_f32, float* lse_out, int32_t* status,
-                                      void* stream) {
-  if (!info) {
-    set_last_error("paged_prefill_gqa: plan info is null");
-    return B200_EINVAL;
-  }
-  if (info->num_items == 0) return B200_OK;
+// Shared launcher.  With `info` the step's item count is known on the host (no launch for an
+// empty plan, a grid no larger than the item list); without it the launch depends only on the
+// device and on num_tokens (the rows q holds), and the kernel reads the count from the plan.
+static int launch_prefill(const char* who, const void* q, int64_t q_stride, const void* key_cache,
+                          const void* value_cache, int num_blocks, int block_size,
+                          const int32_t* block_table, int64_t bt_stride, int32_t* plan_dev,
+                          const b200_prefill_plan_info* info, int num_tokens, int num_q_heads,
+                          int num_kv_heads, int head_dim, float scale, void* out, int out_is_f32,
+                          float* lse_out, int32_t* status, void* stream) {
   if (!q || !key_cache || !value_cache || !block_table || !plan_dev || !out || num_blocks <= 0 ||
-      num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads) {
-    set_last_error("paged_prefill_gqa: null pointer or bad head counts");
+      num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_tokens < 0) {
+    set_last_error("%s: null pointer or bad head counts", who);
     return B200_EINVAL;
   }
   if (head_dim != kPfHeadDim) {
-    set_last_error("paged_prefill_gqa: head_dim %d unsupported (kernel is built for 128)", head_dim);
+    set_last_error("%s: head_dim %d unsupported (kernel is built for 128)", who, head_dim);
     return B200_EUNSUPPORTED;
   }
   if (block_size < 8 || (block_size & (block_size - 1))) {
-    set_last_error("paged_prefill_gqa: block_size %d must be a power of two >= 8", block_size);
+    set_last_error("%s: block_size %d must be a power of two >= 8", who, block_size);
     return B200_EUNSUPPORTED;
   }
   if (reinterpret_cast<uintptr_t>(q) % 16 || (q_stride % 8) || q_stride < (int64_t)num_q_heads * head_dim ||
       reinterpret_cast<uintptr_t>(out) % 16 || reinterpret_cast<uintptr_t>(plan_dev) % 16) {
-    set_last_error("paged_prefill_gqa: q, out and the plan must be 16-byte aligned, the q token stride a multiple of 8 elements and >= Hq*D");
+    set_last_error("%s: q, out and the plan must be 16-byte aligned, the q token stride a multiple of 8 elements and >= Hq*D", who);
     return B200_EALIGN;
   }
   const int box_tokens = block_size < 64 ? block_size : 64;
@@ -775,10 +773,10 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
 
   // One TMA box per Q tile needs a group that divides 128.
   const int group = num_q_heads / num_kv_heads;
-  const bool q_by_tma = kPfRows % group == 0 && info->num_tokens > 0;
+  const bool q_by_tma = kPfRows % group == 0 && num_tokens > 0;
   CUtensorMap q_map = k_map;      // placeholder when the tile is copied row by row
   if (q_by_tma) {
-    rc = get_query_tensor_map(q, info->num_tokens, num_q_heads, q_stride, group, &q_map);
+    rc = get_query_tensor_map(q, num_tokens, num_q_heads, q_stride, group, &q_map);
     if (rc) return rc;
   }
 
@@ -790,7 +788,6 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   p.bt_stride = bt_stride;
   p.items = reinterpret_cast<const PrefillItem*>(plan_dev + kPlanHeaderInts);
   p.work_counter = plan_dev + 2;
-  p.num_items = info->num_items;
   p.out = out;
   p.lse_out = lse_out;
   p.status = status;
@@ -821,8 +818,37 @@ extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const voi
   }
   int grid = b200_sm_count();
   if (grid <= 0) grid = 148;
-  if (grid > info->num_items) grid = info->num_items;
+  if (info && grid > info->num_items) grid = info->num_items;
   return check_cuda(launch_pdl(paged_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), smem_tc,
                                static_cast<cudaStream_t>(stream), k_map, v_map, q_map, p),
                     "paged_prefill_gqa launch");
+}
+
+extern "C" int b200_paged_prefill_gqa(const void* q, int64_t q_stride, const void* key_cache,
+                                      const void* value_cache, int num_blocks, int block_size,
+                                      const int32_t* block_table, int64_t bt_stride,
+                                      int32_t* plan_dev, const b200_prefill_plan_info* info,
+                                      int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                      void* out, int out_is_f32, float* lse_out, int32_t* status,
+                                      void* stream) {
+  if (!info) {
+    set_last_error("paged_prefill_gqa: plan info is null");
+    return B200_EINVAL;
+  }
+  if (info->num_items == 0) return B200_OK;
+  return launch_prefill("paged_prefill_gqa", q, q_stride, key_cache, value_cache, num_blocks, block_size,
+                        block_table, bt_stride, plan_dev, info, info->num_tokens, num_q_heads, num_kv_heads,
+                        head_dim, scale, out, out_is_f32, lse_out, status, stream);
+}
+
+extern "C" int b200_paged_prefill_gqa_replayable(const void* q, int64_t q_stride, const void* key_cache,
+                                                 const void* value_cache, int num_blocks, int block_size,
+                                                 const int32_t* block_table, int64_t bt_stride,
+                                                 int32_t* plan_dev, int num_tokens, int num_q_heads,
+                                                 int num_kv_heads, int head_dim, float scale, void* out,
+                                                 int out_is_f32, float* lse_out, int32_t* status,
+                                                 void* stream) {
+  return launch_prefill("paged_prefill_gqa_replayable", q, q_stride, key_cache, value_cache, num_blocks,
+                        block_size, block_table, bt_stride, plan_dev, nullptr, num_tokens, num_q_heads,
+                        num_kv_heads, head_dim, scale, out, out_is_f32, lse_out, status, stream);
 }

@@ -138,7 +138,7 @@ class B200GraphGqaBackend(B200GqaBackend):
     The plan the capture used is taken out of the backend's pool and belongs to the graph
     from then on (``gear.reg = backend.reg``)."""
 
-    supports_prefill_graph = False      # wide query blocks run eagerly; their launch is sized by the step
+    supports_prefill_graph = True       # the wide-query launch is replayable too (gears of a fixed token count)
 
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
@@ -172,23 +172,30 @@ class B200GraphGqaBackend(B200GqaBackend):
             raise RuntimeError(
                 "capture needs one eager step with the same context first (capturing False): the "
                 "plan's buffers cannot be allocated while the stream is being captured")
-        if meta.prefill is not None:
-            raise NotImplementedError("wide query blocks (prefill chunks) are not captured; "
-                                      "supports_prefill_graph is False")
+        if meta.prefill is not None and not meta.prefill.replayable:
+            raise RuntimeError("the context's prefill plan was not built for replay")
         for key, pooled in list(self._meta_pool.items()):
             if pooled is meta:                      # the plan now belongs to this capture
                 del self._meta_pool[key]
         cache = ctx.kv_caches[layer_idx]
         out = torch.empty(q.shape[0], self.n_q_heads, self.head_dim, dtype=q.dtype, device=q.device)
         ops.paged_decode_gqa(q, cache[0], cache[1], ctx.block_table, meta.decode, self.scale, out=out)
+        if meta.prefill is not None:                # a prefill gear: both launches are recorded
+            ops.paged_prefill_gqa(q, cache[0], cache[1], ctx.block_table, meta.prefill, self.scale, out=out)
         self.reg.append(_GraphRegistration(meta, layer_idx, q, out, cache[0].shape[1]))
         return out
 
     # -- per-step update (graph_fia.py:87-104) --------------------------------
     @staticmethod
     def _refill(meta: StepMetadata, ctx, stream) -> None:
+        captured_prefill = meta.prefill
         with (torch.cuda.stream(stream) if stream is not None else nullcontext()):
             meta.rebuild(ctx.cu_seqlens_q, ctx.seqlens_kv)
+        if meta.prefill is not captured_prefill:
+            if captured_prefill is None:
+                raise ValueError("this graph was captured on a step without wide query blocks: a step with "
+                                 "prefill chunks needs a prefill gear (capture it with such a step)")
+            raise ValueError("the step exceeds the token or sequence count the prefill gear was captured with")
 
     def update(self, ctx, stream=None) -> None:
         self.update_registrations(self.reg, ctx, stream)

@@ -50,11 +50,21 @@ class StepMetadata:
 
     def _plan_prefill(self, causal_base) -> None:
         assert self.decode.skipped_seqs == len(self.prefill_seqs)
+        prefill = getattr(self, "prefill", None)
+        if prefill is not None and prefill.replayable and \
+                self.num_tokens <= prefill.capacity_tokens and len(self.cu_seqlens_q) <= prefill.capacity_seqs:
+            # refilled in place, also with a step that has no wide rows: a launch recorded
+            # against this plan then finds an empty item list
+            prefill.refill(self.cu_seqlens_q, self.seqlens_kv, causal_base)
+            return
         self.prefill = None
         if self.prefill_seqs:
+            replay = self.decode.replayable
             self.prefill = ops.PrefillPlan(self.cu_seqlens_q, self.seqlens_kv, self.num_q_heads,
                                            self.num_kv_heads, self.device, min_rows=16,
-                                           causal_base=causal_base)
+                                           causal_base=causal_base,
+                                           capacity_tokens=self.num_tokens if replay else None,
+                                           capacity_seqs=self.decode.capacity_seqs if replay else None)
 
     @property
     def capacity_seqs(self) -> int:

@@ -322,33 +322,74 @@ def mla_decode_absorbed(q_latent: torch.Tensor, latent_cache: torch.Tensor,
 class PrefillPlan:
     """Host plan + device copy for the wide-query attention kernel: 128-row work
     items of every (sequence, kv head) pair whose q_len * group exceeds
-    ``min_rows``, longest first."""
+    ``min_rows``, longest first.
+
+    With ``capacity_tokens`` (and ``capacity_seqs``) the plan is *replayable*: its device
+    buffer is sized for any step of at most that many query tokens and sequences and keeps
+    its address, ``refill()`` overwrites it in place and the attention launch does not depend
+    on the step, so a CUDA graph that recorded it serves later steps."""
 
     def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_q_heads: int,
                  num_kv_heads: int, device, min_rows: int = 16,
-                 causal_base: Optional[Sequence[int]] = None):
+                 causal_base: Optional[Sequence[int]] = None, capacity_tokens: Optional[int] = None,
+                 capacity_seqs: Optional[int] = None):
         lib = _lib.load()
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("PrefillPlan needs a CUDA device (no CPU fallback)")
+        self.num_q_heads, self.num_kv_heads, self.min_rows = num_q_heads, num_kv_heads, int(min_rows)
         num_seqs = len(cu_seqlens_q)
         num_tokens = int(cu_seqlens_q[-1]) if num_seqs else 0
-        nbytes = lib.b200_prefill_plan_bytes(num_seqs, num_tokens, num_q_heads, num_kv_heads)
-        self.host = torch.empty(max(nbytes // 4, 16), dtype=torch.int32, pin_memory=True)
-        cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
-        kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
-        base_ptr = None
-        if causal_base is not None:
-            base = torch.tensor(list(causal_base), dtype=torch.int32)
-            base_ptr = base.data_ptr()
+        self.replayable = capacity_tokens is not None
+        self.capacity_tokens = max(int(capacity_tokens), num_tokens) if self.replayable else num_tokens
+        self.capacity_seqs = max(int(capacity_seqs or 0), num_seqs) if self.replayable else num_seqs
+        self._nbytes = max(lib.b200_prefill_plan_bytes(self.capacity_seqs, self.capacity_tokens, num_q_heads,
+                                                       num_kv_heads), 64)
+        self._hosts = [torch.empty(self._nbytes // 4, dtype=torch.int32, pin_memory=True)
+                       for _ in range(2 if self.replayable else 1)]
+        self._copied = [None] * len(self._hosts)
+        self._flip = 0
+        self.host = self._hosts[0]
         self.info = PrefillPlanInfo()
-        rc = lib.b200_prefill_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, num_seqs, num_q_heads,
-                                   num_kv_heads, int(min_rows), self.host.data_ptr(),
-                                   self.host.numel() * 4, ctypes.byref(self.info))
-        _lib.check(rc, "b200_prefill_plan")
+        self._build(cu_seqlens_q, seqlens_kv, causal_base)
         used = max(int(self.info.plan_ints), 16)
-        self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
-        self.dev.copy_(self.host[:used], non_blocking=True)
+        self.dev = torch.zeros(self._nbytes // 4 if self.replayable else used, dtype=torch.int32,
+                               device=self.device)
+        self._upload(used)
+
+    def _build(self, cu_seqlens_q, seqlens_kv, causal_base) -> None:
+        lib = _lib.load()
+        num_seqs = len(cu_seqlens_q)
+        num_tokens = int(cu_seqlens_q[-1]) if num_seqs else 0
+        if num_seqs > self.capacity_seqs or num_tokens > self.capacity_tokens:
+            raise ValueError(f"step of {num_seqs} sequences / {num_tokens} tokens exceeds the plan's capacity "
+                             f"({self.capacity_seqs} / {self.capacity_tokens})")
+        int_array = ctypes.c_int32 * max(num_seqs, 1)
+        cu = int_array(*cu_seqlens_q)
+        kv = int_array(*seqlens_kv)
+        base = int_array(*causal_base) if causal_base is not None else None
+        rc = lib.b200_prefill_plan(cu, kv, base, num_seqs, self.num_q_heads, self.num_kv_heads, self.min_rows,
+                                   self.host.data_ptr(), self.host.numel() * 4, ctypes.byref(self.info))
+        _lib.check(rc, "b200_prefill_plan")
+
+    def _upload(self, used: int) -> None:
+        self.dev[:used].copy_(self.host[:used], non_blocking=True)
+        if self.replayable:
+            done = torch.cuda.Event()
+            done.record(torch.cuda.current_stream(self.device))
+            self._copied[self._flip] = done
+
+    def refill(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int],
+               causal_base: Optional[Sequence[int]] = None) -> None:
+        """Plan another step into the same device buffer (see ``DecodePlan.refill``)."""
+        if not self.replayable:
+            raise RuntimeError("refill() needs a plan built with capacity_tokens")
+        self._flip ^= 1
+        self.host = self._hosts[self._flip]
+        if self._copied[self._flip] is not None:
+            self._copied[self._flip].synchronize()
+        self._build(cu_seqlens_q, seqlens_kv, causal_base)
+        self._upload(max(int(self.info.plan_ints), 16))
 
 
 def paged_prefill_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
@@ -375,13 +416,24 @@ def paged_prefill_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: tor
     elif not out.is_contiguous():
         raise ValueError("out must be contiguous")
     with _on_device(q.device):
-        rc = lib.b200_paged_prefill_gqa(
-            q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
-            num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
-            plan.dev.data_ptr(), ctypes.byref(plan.info), n_q, n_kv, d, float(scale),
-            out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
-            lse_out.data_ptr() if lse_out is not None else None,
-            status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        if plan.replayable:
+            if t > plan.capacity_tokens:
+                raise ValueError("q holds more rows than the plan was sized for")
+            rc = lib.b200_paged_prefill_gqa_replayable(
+                q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
+                num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+                plan.dev.data_ptr(), t, n_q, n_kv, d, float(scale),
+                out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+                lse_out.data_ptr() if lse_out is not None else None,
+                status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        else:
+            rc = lib.b200_paged_prefill_gqa(
+                q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
+                num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+                plan.dev.data_ptr(), ctypes.byref(plan.info), n_q, n_kv, d, float(scale),
+                out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+                lse_out.data_ptr() if lse_out is not None else None,
+                status_word(q.device).data_ptr(), _stream_ptr(q.device))
     _lib.check(rc, "b200_paged_prefill_gqa")
     return out
 

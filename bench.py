@@ -159,9 +159,13 @@ def scale_free_ok(out: torch.Tensor, ref: torch.Tensor, atol_rms=2e-2, rtol=2.0 
 
 
 def unroll_for(steps: int) -> int:
-    """Layer-steps recorded per CUDA graph: the largest divisor of ``steps`` up to 10 (an
-    engine replays all layers of a model from one graph, not one graph per layer)."""
-    return max(d for d in range(1, 11) if steps % d == 0)
+    """Layer-steps recorded per CUDA graph (an engine replays all layers of a model from one
+    graph, not one graph per layer): the largest divisor of ``steps`` up to 25, or all of them
+    when ``steps`` is a prime of moderate size."""
+    best = max(d for d in range(1, 26) if steps % d == 0)
+    if best == 1 and 1 < steps <= 64:
+        return steps
+    return best
 
 
 def capture_graph(fn, device, reps: int):

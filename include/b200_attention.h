@@ -214,6 +214,23 @@ int b200_paged_prefill_gqa(const void* q, int64_t q_stride,
                            void* out, int out_is_f32, float* lse_out,
                            int32_t* status, void* stream);
 
+/* The wide-query attention as a launch that can be recorded once and replayed
+ * for other steps (the prefill gears of the reference's graph runner,
+ * auto_infer/worker/graph_decode_runner.py:360-414): the grid is the SM count,
+ * the item count is read from the plan on the device.  plan_dev holds
+ * b200_prefill_plan_bytes(num_seqs, num_tokens, Hq, Hkv) bytes for the largest
+ * step of the gear and is refilled in place (the plan's first info->plan_ints
+ * words) before each replay; q holds num_tokens rows (the gear's static buffer).
+ * A refilled plan with no item at all is fine: every CTA leaves at once. */
+int b200_paged_prefill_gqa_replayable(const void* q, int64_t q_stride,
+                                      const void* key_cache, const void* value_cache,
+                                      int num_blocks, int block_size,
+                                      const int32_t* block_table, int64_t bt_stride,
+                                      int32_t* plan_dev, int num_tokens,
+                                      int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                      void* out, int out_is_f32, float* lse_out,
+                                      int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------ *
  * Same attention as b200_paged_decode_gqa for callers that may not allocate
  * device memory.  (No counterpart in the reference: its vendor op manages its

@@ -113,6 +113,94 @@ def test_one_captured_decode_step_replays_for_other_lengths():
             assert_attention_close(got[live:], ref[live:], what="padding rows")
 
 
+def test_one_captured_prefill_gear_replays_for_other_splits_of_its_tokens():
+    """A prefill gear: a step of 48 query tokens recorded once (slot write, split-KV kernel for
+    the narrow rows, wide-query kernel for the chunks) and replayed for other splits of the 48
+    tokens into sequences - one chunk, two chunks over cached prefixes, decode rows beside a
+    chunk, and a step without any wide row (the recorded wide-query launch then finds no item)."""
+    from auto_infer_b200 import ops, registry
+    from auto_infer_b200.forward_context import ForwardContext
+    dev = torch.device("cuda")
+    tokens, max_seqs = 48, 12
+    cfg = SimpleNamespace(head_dim=HD, num_layers=1, rms_eps=1e-6)
+    model = SimpleNamespace(cfg=cfg, n_q_local=N_Q, n_kv_local=N_KV, w={}, layer_prefix=lambda i: f"model.layers.{i}.",
+                            device=dev, dtype=torch.bfloat16, ATTENTION_FAMILY="gqa")
+    backend, caches = registry.build_attention_backend(model, "graph", NUM_BLOCKS, BS)
+    assert backend.supports_prefill_graph
+    g = torch.Generator().manual_seed(77)
+    for kc, vc in caches:
+        kc.copy_(torch.randn(kc.shape, generator=g).to(torch.bfloat16))
+        vc.copy_(torch.randn(vc.shape, generator=g).to(torch.bfloat16))
+    q = torch.zeros(tokens, N_Q, HD, dtype=torch.bfloat16, device=dev)
+    k_new = torch.zeros(tokens, N_KV, HD, dtype=torch.bfloat16, device=dev)
+    v_new = torch.zeros(tokens, N_KV, HD, dtype=torch.bfloat16, device=dev)
+    slots = torch.zeros(tokens, dtype=torch.int32, device=dev)
+    block_table = torch.zeros(max_seqs, MAX_BLOCKS, dtype=torch.int32, device=dev)
+    perm = torch.randperm(NUM_BLOCKS, generator=g).tolist()
+
+    def stage(seqs):
+        """seqs: (q_len, kv_len) per sequence, kv_len including the q_len new tokens; the gear's
+        unused sequence rows are left without query tokens."""
+        assert sum(q_len for q_len, _ in seqs) == tokens
+        bt = torch.zeros(max_seqs, MAX_BLOCKS, dtype=torch.int32)
+        s_list, cu, kv, acc, cursor = [], [], [], 0, 0
+        for b in range(max_seqs):
+            q_len, kv_len = seqs[b] if b < len(seqs) else (0, 0)
+            need = (kv_len + BS - 1) // BS
+            row = perm[cursor:cursor + need]
+            cursor += need
+            bt[b, :need] = torch.tensor(row, dtype=torch.int32)
+            for pos in range(kv_len - q_len, kv_len):
+                s_list.append(row[pos // BS] * BS + pos % BS)
+            acc += q_len
+            cu.append(acc)
+            kv.append(kv_len)
+        return torch.tensor(s_list, dtype=torch.int32), bt, cu, kv
+
+    def ctx_for(cu, kv):
+        return ForwardContext(None, None, slots, block_table, cu, kv, None, backend, caches, False)
+
+    s0, bt0, cu0, kv0 = stage([(48, 48)])                      # captured on one 48-token prompt
+    slots.copy_(s0)
+    block_table.copy_(bt0)
+    ctx = ctx_for(cu0, kv0)
+    backend.paged_attention(0, q, k_new, v_new, ctx)           # warm-up
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    backend.begin_capture()
+    with torch.cuda.graph(graph):
+        out = backend.paged_attention(0, q, k_new, v_new, ctx)
+    backend.end_capture()
+    gear_reg = backend.reg
+    assert gear_reg[0].meta.prefill is not None and gear_reg[0].meta.prefill.replayable
+
+    splits = [
+        [(48, 48)],                                            # as captured
+        [(30, 130), (18, 18)],                                 # two chunks, one over a cached prefix
+        [(1, 90), (1, 17), (2, 40), (44, 44 + 64)],            # decode rows and a verify pair beside a chunk
+        [(8, 40)] * 6,                                         # six short chunks
+        [(4, 20), (4, 36), (4, 52), (4, 68), (4, 84), (28, 28)],
+        [(4, 20 + 8 * i) for i in range(12)],                  # narrow rows only: the wide-query launch finds no item
+    ]
+    for seqs in splits:
+        s_h, bt_h, cu, kv = stage(seqs)
+        q_h = torch.randn(tokens, N_Q, HD, generator=g).to(torch.bfloat16)
+        k_h = torch.randn(tokens, N_KV, HD, generator=g).to(torch.bfloat16)
+        v_h = torch.randn(tokens, N_KV, HD, generator=g).to(torch.bfloat16)
+        for dst, src in ((q, q_h), (k_new, k_h), (v_new, v_h), (slots, s_h), (block_table, bt_h)):
+            dst.copy_(src)
+        kc, vc = caches[0][0].cpu().clone(), caches[0][1].cpu().clone()
+        backend.update_registrations(gear_reg, ctx_for(cu, kv))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        orc.write_kv(k_h, v_h, kc, vc, s_h.tolist())
+        assert torch.equal(caches[0][0].cpu(), kc) and torch.equal(caches[0][1].cpu(), vc)
+        ref = orc.paged_attention(q_h, kc, vc, bt_h, cu, kv, HD ** -0.5)
+        assert_attention_close(out.cpu(), ref, what=f"split {seqs}")
+    assert gear_reg[0].meta.prefill.info.num_items == 0       # the last split had no wide row
+
+
 def test_capture_without_a_warm_up_step_is_refused():
     from auto_infer_b200.forward_context import ForwardContext
     from auto_infer_b200.gqa import B200GraphGqaBackend

@@ -53,7 +53,7 @@ def test_graph_mode_has_the_lifecycle_surface_the_graph_runners_drive():
     assert caches[0][0].shape == caches[0][1].shape == (5, 16, 2, 128)
     assert caches[0][0].data_ptr() != caches[0][1].data_ptr()
     assert backend.capturing is False and backend.reg == []
-    assert backend.supports_prefill_graph is False
+    assert backend.supports_prefill_graph is True
     backend.begin_capture()
     assert backend.capturing is True and backend.reg == []
     backend.end_capture()
