@@ -50,6 +50,11 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, c_int, c_int, c_int, c_int, c_float,
         c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_paged_decode_gqa_write": (c_int, [
+        c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+        c_int, c_int, c_void_p, c_int64, c_void_p, POINTER(DecodePlanInfo), c_int,
+        c_int, c_int, c_int, c_float,
+        c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_paged_decode_gqa_static": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, POINTER(DecodePlanInfo), c_int, c_int, c_int, c_float,

@@ -78,6 +78,17 @@ struct DecodeParams {
   float scale, scale_log2;
 };
 
+// Fused slot write (the kWrite instantiation): the step's new K/V rows and where they go
+struct WriteParams {
+  const __nv_bfloat16* k_new;
+  const __nv_bfloat16* v_new;
+  int64_t k_new_stride, v_new_stride;   // elements between tokens
+  const int32_t* slot_mapping;
+  __nv_bfloat16* key_cache;
+  __nv_bfloat16* value_cache;
+  int64_t total_slots;
+};
+
 // Walks the CTA's (item, tile) sequence; identical in producer and consumers.
 struct TileWalker {
   const DecodeItem* items;
@@ -150,9 +161,17 @@ __device__ __forceinline__ void merge_noted_pairs(const DecodeParams& p, const i
   }
 }
 
+// kWrite: the form that also performs the step's KV slot write.  The new rows of a sequence
+// (local positions j >= causal_base, row j - causal_base of k_new / v_new) belong to exactly one
+// CTA per kv head - the one that streams the tile they fall in.  Their cache slots have not been
+// written when the tile is loaded, so the warp that owns them puts the rows into the shared-memory
+// tile itself and stores them to their slots in the cache: no write kernel in front of this one.
+// It is an instantiation of its own so that the plain form carries none of its code or registers.
+template <bool kWrite>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
-                        const __grid_constant__ CUtensorMap v_map, const DecodeParams p) {
+                        const __grid_constant__ CUtensorMap v_map, const DecodeParams p,
+                        const WriteParams wp) {
   extern __shared__ uint8_t smem_raw[];
   DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -387,6 +406,31 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
       mbar_wait_bounded(&sm.full[s], (it / kStages) & 1u, abort_flag, p.status);
       const uint32_t kbase = smem_u32(sm.stage[s]);
       const uint32_t vbase = kbase + kTileBytes;
+      if constexpr (kWrite) {
+        const int row_lo = tile * kTileTokens + wslice * 16;
+        const int j_lo = max(max(item.causal_base, 0), row_lo);
+        const int j_hi = min(min(item.kv_len, item.causal_base + item.q_len), row_lo + 16);
+        if (j_lo < j_hi) {
+          const int chunk = lane & 15;                    // 16-byte chunk of the 256-byte row
+          const bool is_v = lane >= 16;                   // lanes 0-15 carry K, lanes 16-31 V
+          for (int j = j_lo; j < j_hi; ++j) {
+            const int64_t tok = item.q_start + (j - item.causal_base);
+            const __nv_bfloat16* src = (is_v ? wp.v_new + tok * wp.v_new_stride : wp.k_new + tok * wp.k_new_stride) +
+                                       item.kv_head * kHeadDim + chunk * 8;
+            const uint4 val = *reinterpret_cast<const uint4*>(src);
+            *reinterpret_cast<uint4*>(sm.stage[s] + (is_v ? kTileBytes : 0) + (chunk >> 3) * kHalfTileBytes +
+                                      swz128(j - tile * kTileTokens, chunk & 7)) = val;
+            const int64_t slot = wp.slot_mapping[tok];
+            if (slot >= 0 && slot < wp.total_slots) {
+              __nv_bfloat16* cache = is_v ? wp.value_cache : wp.key_cache;
+              *reinterpret_cast<uint4*>(cache + (slot * p.num_kv_heads + item.kv_head) * kHeadDim + chunk * 8) = val;
+            } else if (slot >= wp.total_slots && lane == 0 && p.status) {
+              atomicOr(p.status, B200_STATUS_BAD_SLOT);
+            }
+          }
+          __syncwarp();
+        }
+      }
 
       // ---- S = Q K^T for this warp's 16 tokens (two n-tiles of 8)
       float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -471,7 +515,12 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
         mma_bf16_16816(o[2 * j], pf, vb[0], vb[1]);
         mma_bf16_16816(o[2 * j + 1], pf, vb[2], vb[3]);
       }
-      if (ragged) fence_proxy_async();      // the stage goes back to TMA: order these stores before its writes
+      // the stage goes back to TMA: order this warp's stores into it before TMA's writes
+      if constexpr (kWrite) {
+        if (ragged || (tile + 1) * kTileTokens > max(item.causal_base, 0)) fence_proxy_async();
+      } else {
+        if (ragged) fence_proxy_async();
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.empty[s]);
 #ifdef B200_TRACE
@@ -673,13 +722,33 @@ namespace b200 {
 // is launched for an empty plan, the workspace only has to hold the records the plan
 // uses).  Without it every count is read from the plan on the device: the launch then
 // depends on num_ctas alone and can be recorded once and replayed for other steps.
+struct NewKv {
+  const void* k;
+  int64_t k_stride;
+  const void* v;
+  int64_t v_stride;
+  const int32_t* slot_mapping;
+};
+
 static int launch_decode(const char* who, const void* q, int64_t q_stride, const void* key_cache,
                          const void* value_cache, int num_blocks, int block_size,
                          const int32_t* block_table, int64_t bt_stride, int32_t* plan_dev,
                          const b200_decode_plan_info* info, int num_ctas, int num_q_heads,
                          int num_kv_heads, int head_dim, float scale, void* workspace,
                          size_t workspace_bytes, void* out, int out_is_f32, float* lse_out,
-                         int32_t* status, void* stream) {
+                         int32_t* status, void* stream, const NewKv* new_kv = nullptr) {
+  if (new_kv) {
+    if (!new_kv->k || !new_kv->v || !new_kv->slot_mapping) {
+      set_last_error("%s: new K/V rows and the slot mapping must all be given", who);
+      return B200_EINVAL;
+    }
+    if (reinterpret_cast<uintptr_t>(new_kv->k) % 16 || reinterpret_cast<uintptr_t>(new_kv->v) % 16 ||
+        new_kv->k_stride % 8 || new_kv->v_stride % 8 || new_kv->k_stride < (int64_t)num_kv_heads * head_dim ||
+        new_kv->v_stride < (int64_t)num_kv_heads * head_dim) {
+      set_last_error("%s: new K/V rows must be 16-byte aligned with token strides that are multiples of 8 elements", who);
+      return B200_EALIGN;
+    }
+  }
   if (!q || !key_cache || !value_cache || !block_table || !plan_dev || !out || !workspace ||
       num_blocks <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads ||
       num_ctas <= 0) {
@@ -741,21 +810,32 @@ static int launch_decode(const char* who, const void* q, int64_t q_stride, const
   p.out_is_f32 = out_is_f32;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
+  WriteParams wp{};
+  if (new_kv) {
+    wp.k_new = static_cast<const __nv_bfloat16*>(new_kv->k);
+    wp.v_new = static_cast<const __nv_bfloat16*>(new_kv->v);
+    wp.k_new_stride = new_kv->k_stride;
+    wp.v_new_stride = new_kv->v_stride;
+    wp.slot_mapping = new_kv->slot_mapping;
+    wp.key_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(key_cache));
+    wp.value_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(value_cache));
+    wp.total_slots = (int64_t)num_blocks * block_size;
+  }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = sizeof(DecodeSmem) + 1024;
-  static bool attr_set[64] = {false};
+  static bool attr_set[2][64] = {{false}, {false}};
+  auto kernel = new_kv ? paged_decode_gqa_kernel<true> : paged_decode_gqa_kernel<false>;
+  const int which = new_kv ? 1 : 0;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 64 || !attr_set[dev]) {
-    rc = check_cuda(cudaFuncSetAttribute(paged_decode_gqa_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+  if (dev >= 64 || !attr_set[which][dev]) {
+    rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                     "paged_decode_gqa smem attribute");
     if (rc) return rc;
-    if (dev < 64) attr_set[dev] = true;
+    if (dev < 64) attr_set[which][dev] = true;
   }
-  return check_cuda(launch_pdl(paged_decode_gqa_kernel, dim3(num_ctas), dim3(kDecodeThreads), smem, s,
-                               k_map, v_map, p),
+  return check_cuda(launch_pdl(kernel, dim3(num_ctas), dim3(kDecodeThreads), smem, s, k_map, v_map, p, wp),
                     "paged_decode_gqa launch");
 }
 
@@ -794,6 +874,30 @@ extern "C" int b200_paged_decode_gqa_replayable(const void* q, int64_t q_stride,
                        block_size, block_table, bt_stride, plan_dev, nullptr, num_ctas, num_q_heads,
                        num_kv_heads, head_dim, scale, workspace, workspace_bytes, out, out_is_f32,
                        lse_out, status, stream);
+}
+
+extern "C" int b200_paged_decode_gqa_write(const void* q, int64_t q_stride, const void* k_new,
+                                           int64_t k_new_stride, const void* v_new, int64_t v_new_stride,
+                                           const int32_t* slot_mapping, void* key_cache, void* value_cache,
+                                           int num_blocks, int block_size, const int32_t* block_table,
+                                           int64_t bt_stride, int32_t* plan_dev,
+                                           const b200_decode_plan_info* info, int num_ctas,
+                                           int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                           void* workspace, size_t workspace_bytes, void* out,
+                                           int out_is_f32, float* lse_out, int32_t* status, void* stream) {
+  using namespace b200;
+  if (info && info->skipped_seqs != 0) {
+    set_last_error("paged_decode_gqa_write: the plan leaves %d sequences to the wide-query kernel, whose new "
+                   "rows this call would not write; use b200_reshape_and_cache for such a step",
+                   info->skipped_seqs);
+    return B200_EUNSUPPORTED;
+  }
+  if (info && info->num_items == 0) return B200_OK;
+  NewKv nk{k_new, k_new_stride, v_new, v_new_stride, slot_mapping};
+  return launch_decode("paged_decode_gqa_write", q, q_stride, key_cache, value_cache, num_blocks, block_size,
+                       block_table, bt_stride, plan_dev, info, info ? info->num_ctas : num_ctas, num_q_heads,
+                       num_kv_heads, head_dim, scale, workspace, workspace_bytes, out, out_is_f32, lse_out,
+                       status, stream, &nk);
 }
 
 // ---------------------------------------------------------------------------

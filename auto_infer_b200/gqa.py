@@ -26,6 +26,8 @@ class B200GqaBackend(AttentionBackend):
     match ``GqaFIABackend`` (gqa.py:56-74), so the registry builder can pass the
     same keyword set."""
 
+    _one_launch_step = True           # paged_attention may fold the slot write into the attention launch
+
     def __init__(self, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                  num_layers: int, device, dtype, w: dict = None, layer_prefix=None, rms_eps=None,
                  tp_group=None):
@@ -102,7 +104,15 @@ class B200GqaBackend(AttentionBackend):
     def paged_attention(self, layer_idx: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                         ctx) -> torch.Tensor:
         """Cache write followed by attention for already projected and rotated
-        q/k/v: the part of ``attention`` this package accelerates."""
+        q/k/v: the part of ``attention`` this package accelerates.  A step of decode-shaped
+        rows only (no chunk for the wide-query kernel) is one launch: the attention kernel
+        stores the new rows itself."""
+        cache = ctx.kv_caches[layer_idx]
+        meta = step_metadata(ctx, self.n_q_heads, self.n_kv_heads, self.head_dim, q.device,
+                             pool=self._meta_pool)
+        if meta.prefill is None and meta.decode.info.num_items and self._one_launch_step:
+            return ops.paged_decode_gqa_write(q, k, v, ctx.slot_mapping, cache[0], cache[1], ctx.block_table,
+                                              meta.decode, self.scale)
         self._write_kv(layer_idx, k, v, ctx)
         return self._attn(layer_idx, q, k, v, ctx)
 
@@ -139,6 +149,8 @@ class B200GraphGqaBackend(B200GqaBackend):
     from then on (``gear.reg = backend.reg``)."""
 
     supports_prefill_graph = True       # the wide-query launch is replayable too (gears of a fixed token count)
+
+    _one_launch_step = False          # the recorded launches go through _write_kv / _attn
 
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)

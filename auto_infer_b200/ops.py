@@ -246,6 +246,54 @@ def paged_decode_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torc
     return out
 
 
+def paged_decode_gqa_write(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                           slot_mapping: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                           block_table: torch.Tensor, plan: DecodePlan, scale: float,
+                           out: Optional[torch.Tensor] = None, out_f32: bool = False,
+                           lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``write_kv`` + ``paged_fia`` of a decode-shaped step in one launch
+    (auto_infer/layers/attention/base.py:41-61): the CTA that streams the KV tile a new row
+    falls in takes the row from ``k_new`` / ``v_new`` and stores it to its slot itself.  Same
+    bits as ``reshape_and_cache`` followed by ``paged_decode_gqa``.  The plan must cover every
+    sequence of the step (no rows left to the wide-query kernel)."""
+    _need_cuda(q, k_new, v_new, slot_mapping, key_cache, value_cache, block_table)
+    lib = _lib.load()
+    t, n_q, d = q.shape
+    if plan.info.skipped_seqs:
+        raise ValueError("the plan leaves sequences to the wide-query kernel: write their rows with "
+                         "reshape_and_cache and attend with paged_decode_gqa / paged_prefill_gqa")
+    if q.stride(2) != 1 or q.stride(1) != d:
+        q = q.contiguous()
+    for name, x in (("k_new", k_new), ("v_new", v_new)):
+        if x.shape[0] != t or x.stride(2) != 1 or x.stride(1) != d:
+            raise ValueError(f"{name}: (T, Hkv, D) with each token's heads contiguous")
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("KV caches must be contiguous (num_blocks, block_size, Hkv, D)")
+    num_blocks, block_size, n_kv, _ = key_cache.shape
+    if block_table.dtype != torch.int32:
+        block_table = block_table.to(torch.int32)
+    if block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+    if slot_mapping.dtype != torch.int32 or not slot_mapping.is_contiguous():
+        slot_mapping = slot_mapping.to(torch.int32).contiguous()
+    if out is None:
+        out = torch.empty(t, n_q, d, dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
+    elif not out.is_contiguous():
+        raise ValueError("out must be contiguous")
+    with _on_device(q.device):
+        rc = lib.b200_paged_decode_gqa_write(
+            q.data_ptr(), q.stride(0), k_new.data_ptr(), k_new.stride(0), v_new.data_ptr(), v_new.stride(0),
+            slot_mapping.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+            num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+            plan.dev.data_ptr(), None if plan.replayable else ctypes.byref(plan.info), plan.num_ctas,
+            n_q, n_kv, d, float(scale), plan.workspace.data_ptr(), plan.workspace.numel(), out.data_ptr(),
+            1 if out.dtype == torch.float32 else 0,
+            lse_out.data_ptr() if lse_out is not None else None,
+            status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "b200_paged_decode_gqa_write")
+    return out
+
+
 class MlaDecodePlan:
     """Host plan + device copy + workspace of the absorbed-MLA decode kernel
     (32-token latent tiles, one shared latent head)."""

@@ -311,10 +311,8 @@ def side_config(name, device):
     caches = [b.kv_cache] + [b.kv_cache.clone() for _ in range(layers - 1)]
 
     def make(i):
-        def step():
-            ops.reshape_and_cache(b.k_new, b.v_new, caches[i][0], caches[i][1], b.slot_mapping)
-            ops.paged_decode_gqa(b.q, caches[i][0], caches[i][1], b.block_table, plan, b.scale, out=out)
-        return step
+        return lambda: ops.paged_decode_gqa_write(b.q, b.k_new, b.v_new, b.slot_mapping, caches[i][0],
+                                                  caches[i][1], b.block_table, plan, b.scale, out=out)
 
     us, best = layer_rotation_time(make, layers, device)
     bytes_ = b.kv_bytes() + 2 * b.q.numel() * 2
@@ -452,6 +450,10 @@ def profile_case(args):
         out = torch.empty(b.q.shape, dtype=torch.bfloat16, device=dev)
 
         def step():
+            if meta.prefill is None:
+                ops.paged_decode_gqa_write(b.q, b.k_new, b.v_new, b.slot_mapping, b.kv_cache[0], b.kv_cache[1],
+                                           b.block_table, meta.decode, b.scale, out=out)
+                return
             ops.reshape_and_cache(b.k_new, b.v_new, b.kv_cache[0], b.kv_cache[1], b.slot_mapping)
             ops.paged_decode_gqa(b.q, b.kv_cache[0], b.kv_cache[1], b.block_table, meta.decode,
                                  b.scale, out=out)
@@ -530,7 +532,15 @@ def main():
         if owner_of_new_token:
             ops.reshape_and_cache(b.k_new, b.v_new, k_cache, v_cache, b.slot_mapping)
 
+    def one_launch_step():
+        # one GPU: slot write and attention are one launch (the CTA that streams the tile the
+        # new row falls in stores it); this is also the dominant kernel the roofline is about
+        return ops.paged_decode_gqa_write(b.q, b.k_new, b.v_new, b.slot_mapping, k_cache, v_cache,
+                                          b.block_table, cpd.meta.decode, b.scale, out=cpd.out)
+
     def layer_step():
+        if world == 1:
+            return one_launch_step()
         write_new_token()
         return cpd.attend(b.q, k_cache, v_cache, b.block_table, b.scale)
 
@@ -539,7 +549,7 @@ def main():
             ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, cpd.meta.decode, b.scale,
                                  out=cpd.partial.o, lse_out=cpd.partial.lse)
         else:
-            ops.paged_decode_gqa(b.q, k_cache, v_cache, b.block_table, cpd.meta.decode, b.scale, out=cpd.out)
+            one_launch_step()
 
     def barrier():
         if world > 1:
@@ -591,7 +601,7 @@ def main():
     batches = timed_batches(run_steps, args.steps, barrier, n_batches)
     ms_per_step = max_over_ranks(statistics.median(batches), device, world) / args.steps
     value = total_kv_bytes / (ms_per_step * 1e-3) / 1e12
-    launches_per_step = (1 if owner_of_new_token else 0) + 1 + (1 if world > 1 else 0)
+    launches_per_step = 1 if world == 1 else (1 if owner_of_new_token else 0) + 2
 
     # ---- the dominant kernel alone, replayed the same way, for the roofline -------------
     run_kernel(unroll * 2)

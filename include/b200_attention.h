@@ -175,6 +175,45 @@ int b200_paged_decode_gqa_replayable(const void* q, int64_t q_stride,
                                      int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------ *
+ * Slot write and attention of a step in one launch.  Replaces the pair
+ * write_kv + paged_fia that every layer issues back to back
+ * (auto_infer/layers/attention/base.py:41-61, called from
+ * layers/attention/gqa.py:94-113): the new K/V rows of a sequence are the last
+ * q_len keys of its own attention, so the CTA that streams the KV tile they fall
+ * in takes them from k_new / v_new instead of from the (not yet written) cache
+ * rows, and stores them to their slots itself.  One kernel less per layer and
+ * no wait between the write and the first tile load.
+ *   k_new / v_new (T, Hkv, 128) bf16, token strides k_new_stride / v_new_stride
+ *       elements (multiples of 8, 16-byte aligned bases): row t of the packed
+ *       query is the key at position kv_len - q_len + (t - q_start) of its
+ *       sequence;
+ *   slot_mapping (T,) int32 as b200_reshape_and_cache (negative: the row is
+ *       not stored - it still takes part in the attention; past the pool:
+ *       B200_STATUS_BAD_SLOT);
+ *   key_cache / value_cache are written; everything else as
+ *       b200_paged_decode_gqa.  With info == NULL the launch is the replayable
+ *       one (grid num_ctas, counts read from the plan).
+ * The result equals b200_reshape_and_cache followed by b200_paged_decode_gqa bit
+ * for bit, provided slot_mapping names the rows the block table gives for those
+ * positions (the reference computes both from the same table,
+ * auto_infer/worker/model_runner.py:100-124).  Only sequences the plan covers are
+ * written: a plan with info->skipped_seqs != 0 is refused (B200_EUNSUPPORTED);
+ * with info == NULL that is the caller's to ensure.  Not for context-parallel
+ * plans (a rank's causal_base is shifted there). */
+int b200_paged_decode_gqa_write(const void* q, int64_t q_stride,
+                                const void* k_new, int64_t k_new_stride,
+                                const void* v_new, int64_t v_new_stride,
+                                const int32_t* slot_mapping,
+                                void* key_cache, void* value_cache,
+                                int num_blocks, int block_size,
+                                const int32_t* block_table, int64_t bt_stride,
+                                int32_t* plan_dev, const b200_decode_plan_info* info, int num_ctas,
+                                int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                void* workspace, size_t workspace_bytes,
+                                void* out, int out_is_f32, float* lse_out,
+                                int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
  * Paged GQA attention for wide query blocks: chunked prefill over a cached
  * prefix and multi-token verify, any q_len, bottom-right causal.  Replaces
  * paged_fia (auto_infer/layers/attention/base.py:48-61) for the rows the decode
