@@ -29,6 +29,12 @@ class PrefillPlanInfo(ctypes.Structure):
     _fields_ = [(name, c_int32) for name in ("num_items", "total_tiles", "plan_ints", "num_tokens")]
 
 
+class MhaPlanInfo(ctypes.Structure):
+    """Mirror of ``b200_mha_plan_info``."""
+    _fields_ = [("num_items", c_int32), ("num_splits", c_int32), ("num_tokens", c_int32),
+                ("plan_ints", c_int32), ("total_tiles", c_int64)]
+
+
 # name -> (restype, argtypes); one entry per function the header declares
 SIGNATURES = {
     "b200_version": (c_char_p, []),
@@ -71,6 +77,15 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, c_int, c_int, c_int, c_int, c_float,
         c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_mha_plan_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "b200_mha_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "b200_mha_plan": (c_int, [
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+        c_void_p, c_size_t, POINTER(MhaPlanInfo)]),
+    "b200_paged_mha": (c_int, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+        c_void_p, POINTER(MhaPlanInfo), c_int, c_int, c_int, c_float,
+        c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_mla_decode_plan": (c_int, [
         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
         c_void_p, c_size_t, POINTER(DecodePlanInfo)]),

@@ -25,7 +25,7 @@ SOURCES = [
     "lse_combine.cu",
     "cp_exchange.cu",
     "copy_blocks.cu",
-    "rope_cache.cu",
+    "rope_cache.cu", "paged_mha.cu",
 ]
 
 NVCC_FLAGS = [

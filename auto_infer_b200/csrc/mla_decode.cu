@@ -31,6 +31,10 @@ constexpr int kMlaSub = kLatentDim / 64;                      // 64-dim sub-tile
 constexpr int kMlaSubBytes = kMlaTileTokens * 128;            // [32 tokens][64 dims] bf16
 constexpr int kMlaStageBytes = kMlaSub * kMlaSubBytes;        // 36 864
 constexpr int kMlaStages = 4;
+// Tiles alternate between the two consumer groups.  With an even ring a group meets every
+// phase of the stages it uses; with an odd ring it would meet every other phase only, and a
+// parity wait cannot tell phase k from phase k + 2: a group running ahead would read a stage
+// before its tile has landed.
 static_assert(kMlaStages % 2 == 0, "each stage must always be consumed by the same warp group");
 constexpr int kMlaWarps = 8;
 constexpr int kMlaConsumerThreads = kMlaWarps * 32;

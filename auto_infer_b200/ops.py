@@ -486,6 +486,82 @@ def paged_prefill_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: tor
     return out
 
 
+class MhaPlan:
+    """Host plan + device copy + workspace of the K-192 / V-128 multi-head kernel (non-absorbed
+    MLA): blocks of 64 query positions per head, keys cut into equal splits when the step has
+    too few blocks for the SMs."""
+
+    def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_heads: int, device,
+                 num_ctas: Optional[int] = None, causal_base: Optional[Sequence[int]] = None):
+        lib = _lib.load()
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("MhaPlan needs a CUDA device (no CPU fallback)")
+        num_seqs = len(cu_seqlens_q)
+        num_tokens = int(cu_seqlens_q[-1]) if num_seqs else 0
+        self.num_heads = num_heads
+        self.num_ctas = int(num_ctas) if num_ctas else sm_count(self.device)
+        nbytes = lib.b200_mha_plan_bytes(num_seqs, num_tokens, num_heads)
+        self.host = torch.empty(max(nbytes // 4, 16), dtype=torch.int32, pin_memory=True)
+        cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
+        kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
+        base_ptr = None
+        if causal_base is not None:
+            base = torch.tensor(list(causal_base), dtype=torch.int32)
+            base_ptr = base.data_ptr()
+        self.info = _lib.MhaPlanInfo()
+        rc = lib.b200_mha_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, num_seqs, num_heads, self.num_ctas,
+                               self.host.data_ptr(), self.host.numel() * 4, ctypes.byref(self.info))
+        _lib.check(rc, "b200_mha_plan")
+        used = max(int(self.info.plan_ints), 16)
+        self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
+        self.dev.copy_(self.host[:used], non_blocking=True)
+        self.workspace = None
+        if self.info.num_splits > 1:
+            ws = int(self.info.num_splits) * num_tokens * num_heads * (128 + 1) * 4 + 16
+            self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
+
+
+def paged_mha(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor, block_table: torch.Tensor,
+              plan: MhaPlan, scale: float, out: Optional[torch.Tensor] = None, out_f32: bool = False,
+              lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged attention of the non-absorbed MLA form (auto_infer/layers/attention/mla.py:56-63,
+    243-254): q (T, H, 192) over key_cache (num_blocks, block_size, H, 192) and value_cache
+    (num_blocks, block_size, H, 128) -> (T, H, 128); decode rows and prefill chunks alike."""
+    _need_cuda(q, key_cache, value_cache, block_table)
+    lib = _lib.load()
+    t, h, dk = q.shape
+    if q.stride(2) != 1 or q.stride(1) != dk:
+        q = q.contiguous()
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("KV caches must be contiguous (num_blocks, block_size, H, D)")
+    num_blocks, block_size, n_kv, _ = key_cache.shape
+    dv = value_cache.shape[3]
+    if n_kv != h or value_cache.shape[:3] != key_cache.shape[:3]:
+        raise ValueError("one K and one V row per query head: caches (num_blocks, block_size, H, 192 / 128)")
+    if t != plan.info.num_tokens:
+        raise ValueError(f"the plan covers {plan.info.num_tokens} tokens, q has {t}")
+    if block_table.dtype != torch.int32:
+        block_table = block_table.to(torch.int32)
+    if block_table.stride(1) != 1:
+        block_table = block_table.contiguous()
+    if out is None:
+        out = torch.empty(t, h, dv, dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
+    elif not out.is_contiguous():
+        raise ValueError("out must be contiguous")
+    ws = plan.workspace
+    with _on_device(q.device):
+        rc = lib.b200_paged_mha(
+            q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(), num_blocks, block_size,
+            block_table.data_ptr(), block_table.stride(0), plan.dev.data_ptr(), ctypes.byref(plan.info),
+            h, dk, dv, float(scale), ws.data_ptr() if ws is not None else None,
+            ws.numel() if ws is not None else 0, out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+            lse_out.data_ptr() if lse_out is not None else None,
+            status_word(q.device).data_ptr(), _stream_ptr(q.device))
+    _lib.check(rc, "b200_paged_mha")
+    return out
+
+
 def lse_combine(o_parts: torch.Tensor, lse_parts: torch.Tensor,
                 out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None,
                 lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:

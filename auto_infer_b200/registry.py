@@ -63,17 +63,21 @@ def _gqa_mtp(model, mode: str, prefix: str):
 
 
 def _mla(model, mode: str):
-    from .mla import B200MlaBackend
+    from .mla import B200MlaBackend, B200MlaPagedBackend
     if mode == "dense":
         _dense_unavailable("mla")
     cfg = model.cfg
-    # the reference keeps the absorbed form off because its vendor op rejects a
-    # 576-wide head (auto_infer/models/deepseek_v2.py:62-64); here it is the form built
-    return B200MlaBackend(
+    # The reference keeps the absorbed form off by default because its vendor op rejects a
+    # 576-wide head (auto_infer/models/deepseek_v2.py:62-64); here it is the default.  A model
+    # that sets ``_mla_b200_absorb = False`` keeps the reference's per-head K 192 / V 128
+    # caches (auto_infer/layers/attention/registry.py:80-85 reads ``_mla_absorb`` the same way).
+    absorb = getattr(model, "_mla_b200_absorb", True)
+    cls = B200MlaBackend if absorb else B200MlaPagedBackend
+    return cls(
         model.w, num_heads=cfg.num_heads, qk_nope=cfg.qk_nope, qk_rope=cfg.qk_rope,
         v_head_dim=cfg.v_head_dim, kv_lora_rank=cfg.kv_lora_rank, q_lora_rank=cfg.q_lora_rank,
         rms_eps=cfg.rms_eps, softmax_scale=model._softmax_scale, num_layers=cfg.num_layers,
-        device=model.device, dtype=model.dtype, absorb=True, layer_prefix=model.layer_prefix)
+        device=model.device, dtype=model.dtype, absorb=absorb, layer_prefix=model.layer_prefix)
 
 
 register_attention_family("gqa", _gqa)

@@ -17,7 +17,7 @@ reported beside it.  Rank 0 prints one JSON line.
 (restated for paged KV in oracle/) on the host cores, one sequence of the batch
 per step.
 
-``--case c1|c2|c3|c4|decode --iters N`` runs the kernels of one workload N times
+``--case c1|c2|c3|c4|decode|mha --iters N`` runs the kernels of one workload N times
 on a bounded case and exits (what the profiler commands under profiles/ run).
 """
 from __future__ import annotations
@@ -59,7 +59,7 @@ def parse_args():
                     help="context-parallel exchange: fused peer-to-peer kernel or NCCL all-gather")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the step's kernels one by one instead of replaying a CUDA graph")
-    ap.add_argument("--case", default=None, choices=["decode", "c1", "c2", "c3", "c4", "merges"],
+    ap.add_argument("--case", default=None, choices=["decode", "c1", "c2", "c3", "c4", "merges", "mha"],
                     help="profiler mode: run one workload's kernels --iters times and exit")
     ap.add_argument("--iters", type=int, default=3)
     return ap.parse_args()
@@ -429,6 +429,31 @@ def profile_case(args):
             ops.mla_rope_norm_cache(ckv, torch.ones(512, dtype=torch.bfloat16, device=dev), 1e-6, qm[..., 128:],
                                     ql[..., 512:], cs64, sn64, lat, slots)
             ops.copy_blocks([cache], [cache2], ids)
+    elif args.case == "mha":
+        # config 3's sequences (16 heads, contexts 1 024-8 192) in the reference's default,
+        # non-absorbed cache layout: per head K 192 / V 128
+        b3 = synth.config3(batch if args.batch else 16)
+        name = "non-absorbed MLA decode, K 192 / V 128 per head, lengths of " + b3.name
+        lens, bs = b3.seqlens_kv, b3.block_size
+        del b3
+        pages = [(n + bs - 1) // bs for n in lens]
+        pool = sum(pages)
+        g = torch.Generator(device=dev).manual_seed(5)
+        order = torch.randperm(pool, generator=torch.Generator().manual_seed(5)).to(torch.int32)
+        table = torch.zeros(len(lens), max(pages), dtype=torch.int32)
+        at = 0
+        for i, n in enumerate(pages):
+            table[i, :n] = order[at:at + n]
+            at += n
+        table = table.to(dev)
+        kc = torch.randn(pool, bs, 16, 192, generator=g, device=dev).to(torch.bfloat16)
+        vc = torch.randn(pool, bs, 16, 128, generator=g, device=dev).to(torch.bfloat16)
+        qh = torch.randn(len(lens), 16, 192, generator=g, device=dev).to(torch.bfloat16)
+        plan = ops.MhaPlan(list(range(1, len(lens) + 1)), lens, 16, dev)
+        out = torch.empty(len(lens), 16, 128, dtype=torch.bfloat16, device=dev)
+
+        def step():
+            ops.paged_mha(qh, kc, vc, table, plan, 192 ** -0.5, out=out)
     elif args.case == "c3":
         b = synth.config3(batch if args.batch else 64, dev)
         name = b.name

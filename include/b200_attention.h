@@ -17,6 +17,7 @@
  *   b200_paged_decode_gqa       auto_infer/layers/attention/base.py:48-61   (paged_fia, q_len*group <= 16)
  *   b200_paged_prefill_gqa      auto_infer/layers/attention/base.py:48-61   (paged_fia, any q_len)
  *   b200_mla_decode_absorbed    auto_infer/layers/attention/mla.py:115-120  (paged_fia over the 576-wide latent)
+ *   b200_paged_mha              auto_infer/layers/attention/mla.py:56-63    (paged_fia, K 192 / V 128 per head)
  *   b200_lse_combine            no vendor counterpart; merges what graph_fia.py:41 calls [o, lse]
  *   b200_decode_plan*           host-side replacement of the per-step host length lists
  *                               (auto_infer/worker/model_runner.py:126-136)
@@ -337,6 +338,50 @@ int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
                              void* workspace, size_t workspace_bytes,
                              void* out, int out_is_f32, float* lse_out,
                              int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------ *
+ * Paged attention of the non-absorbed MLA form: one decompressed K (192 wide,
+ * [k_nope | k_pe]) and V (128 wide) row per head and token, every query head
+ * its own kv head.  Replaces the paged_fia call of mla_paged and of
+ * MlaFIABackend._attn (auto_infer/layers/attention/mla.py:56-63, 243-254) with
+ * the caches of MlaFIABackend.alloc_kv_caches (mla.py:214-216):
+ *   key_cache (num_blocks, block_size, H, 192), value_cache (.., H, 128) bf16
+ *   q (T, H, 192) bf16, token stride q_stride elements (even)
+ *   out (T, H, 128) bf16 or fp32; lse_out (T, H) or NULL
+ * Decode rows and prefill chunks of any q_len in one launch, bottom-right
+ * causal; causal_base as in b200_decode_plan.  The host plan cuts every
+ * sequence into blocks of 64 query positions per head and, when that gives too
+ * few items for the SMs, every block's keys into up to 8 equal splits whose
+ * normalised rows are merged by b200_lse_combine (launched by this call).
+ *   plan buffer: b200_mha_plan_bytes(num_seqs, num_tokens, H) bytes (upper bound)
+ *   workspace:   b200_mha_workspace_bytes(num_tokens, H) bytes (used when the
+ *                plan has more than one split; may be NULL otherwise)
+ * Cache rows past a sequence's kv_len may hold any bytes. */
+typedef struct b200_mha_plan_info {
+  int32_t num_items;     /* CTAs of the launch                                   */
+  int32_t num_splits;    /* key splits per (block of rows, head), 1..8           */
+  int32_t num_tokens;    /* packed query tokens the plan covers                  */
+  int32_t plan_ints;     /* int32 words of the plan to copy to the device        */
+  int64_t total_tiles;   /* 64-token tiles streamed by all items                 */
+} b200_mha_plan_info;
+
+size_t b200_mha_plan_bytes(int num_seqs, int num_tokens, int num_heads);
+size_t b200_mha_workspace_bytes(int num_tokens, int num_heads);
+
+int b200_mha_plan(const int32_t* cu_seqlens_q_host, const int32_t* seqlens_kv_host,
+                  const int32_t* causal_base_host,
+                  int num_seqs, int num_heads, int num_ctas,
+                  int32_t* plan_host, size_t plan_bytes, b200_mha_plan_info* info);
+
+int b200_paged_mha(const void* q, int64_t q_stride,
+                   const void* key_cache, const void* value_cache,
+                   int num_blocks, int block_size,
+                   const int32_t* block_table, int64_t bt_stride,
+                   const int32_t* plan_dev, const b200_mha_plan_info* info,
+                   int num_heads, int k_dim, int v_dim, float scale,
+                   void* workspace, size_t workspace_bytes,
+                   void* out, int out_is_f32, float* lse_out,
+                   int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------ *
  * Merge n_parts normalised partial results by log-sum-exp:

@@ -39,3 +39,9 @@ def golden_small():
 def golden_paged():
     import torch
     return torch.load(os.path.join(GOLDEN, "reference_paged.pt"), weights_only=False)
+
+
+@pytest.fixture(scope="session")
+def golden_mla_paged():
+    import torch
+    return torch.load(os.path.join(GOLDEN, "reference_mla_paged.pt"), weights_only=False)

@@ -190,6 +190,94 @@ def mla_cases():
                 lat576=dict(seqs=seqs, scale=scale2, latent=lat_tokens, q=q_lat, o=o_lat))
 
 
+def _install_vendor_norm_stub():
+    """The reference's RMSNorm (auto_infer/layers/norm.py:5-9) is a call into the vendor module,
+    which does not exist off the NPU.  The one function of it the MLA sub-block needs is stood
+    in for here, by its documented arithmetic (normalise in fp32, round to the input type,
+    scale by the weight); everything else in these fixtures is the reference's own code."""
+    import types
+    if "torch_npu" in sys.modules:
+        return
+    stub = types.ModuleType("torch_npu")
+
+    def npu_rms_norm(x, weight, eps):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * weight, None
+
+    stub.npu_rms_norm = npu_rms_norm
+    sys.modules["torch_npu"] = stub
+
+
+def mla_paged_cases():
+    """Non-absorbed MLA at the real head widths (K 192 = 128 + 64, V 128): the reference's
+    whole sub-block (``MlaDenseBackend.attention``: q-LoRA or plain q projection, kv_a, latent
+    norm, kv_b, interleaved rotary embedding, per-head K / V, causal softmax, o_proj) on
+    packed prefill sequences, the q / k / v it hands to its core, and decode / verify rows
+    of the core obtained by zero-padding the query."""
+    _install_vendor_norm_stub()
+    out = {}
+    for name, q_lora in (("plain_q", None), ("q_lora", 48)):
+        g = torch.Generator().manual_seed(31 if q_lora is None else 32)
+        nh, nope, rope, vd, kvl, hidden = 4, 128, 64, 128, 64, 96
+        scale = (nope + rope) ** -0.5
+        p = "model.layers.0.self_attn."
+
+        def rnd(*shape, s=0.08):
+            return (torch.randn(*shape, generator=g) * s).to(torch.bfloat16)
+
+        w = {p + "kv_a_proj_with_mqa.weight": rnd(kvl + rope, hidden),
+             p + "kv_a_layernorm.weight": (1 + 0.1 * torch.randn(kvl, generator=g)).to(torch.bfloat16),
+             p + "kv_b_proj.weight": rnd(nh * (nope + vd), kvl, s=0.15),
+             p + "o_proj.weight": rnd(hidden, nh * vd)}
+        if q_lora is None:
+            w[p + "q_proj.weight"] = rnd(nh * (nope + rope), hidden)
+        else:
+            w[p + "q_a_proj.weight"] = rnd(q_lora, hidden)
+            w[p + "q_a_layernorm.weight"] = (1 + 0.1 * torch.randn(q_lora, generator=g)).to(torch.bfloat16)
+            w[p + "q_b_proj.weight"] = rnd(nh * (nope + rope), q_lora, s=0.15)
+        lens = [70, 9, 130]
+        total = sum(lens)
+        x = torch.randn(total, hidden, generator=g).to(torch.bfloat16)
+        pos = torch.cat([torch.arange(n, dtype=torch.float32) for n in lens])
+        inv = 1.0 / (10000.0 ** (torch.arange(0, rope, 2, dtype=torch.float32) / rope))
+        ang = torch.cat([pos[:, None] * inv[None], pos[:, None] * inv[None]], dim=-1)
+        cos = ang.cos()[:, None, :].to(torch.bfloat16)
+        sin = ang.sin()[:, None, :].to(torch.bfloat16)
+        backend = MlaDenseBackend(w, num_heads=nh, qk_nope=nope, qk_rope=rope, v_head_dim=vd,
+                                  kv_lora_rank=kvl, q_lora_rank=q_lora, rms_eps=1e-6, softmax_scale=scale)
+        seen = {}
+        core = backend._attn
+
+        def spy(layer_idx, q, k, v, ctx):
+            seen["q"], seen["k"], seen["v"] = q.clone(), k.clone(), v.clone()
+            seen["o"] = core(layer_idx, q, k, v, ctx)
+            return seen["o"]
+
+        backend._attn = spy
+        ctx = _Ctx()
+        ctx.cu_seqlens_q = [int(c) for c in np.cumsum(lens)]
+        ctx.cos, ctx.sin = cos, sin
+        block_out = backend.attention(0, x, ctx)
+        out[name] = dict(nh=nh, nope=nope, rope=rope, vd=vd, kvl=kvl, hidden=hidden, q_lora=q_lora,
+                         scale=scale, w=w, x=x, cos=cos, sin=sin, cu=ctx.cu_seqlens_q, lens=lens,
+                         q=seen["q"], k=seen["k"], v=seen["v"], core_out=seen["o"], block_out=block_out)
+
+    # decode (q_len 1) and verify (q_len 3) rows of the core over longer sequences
+    g = torch.Generator().manual_seed(33)
+    nh, scale = 4, 192 ** -0.5
+    rows = []
+    for q_len, kv_len in ((1, 200), (3, 131), (1, 64), (2, 65)):
+        k = torch.randn(kv_len, nh, 192, generator=g).to(torch.bfloat16)
+        v = torch.randn(kv_len, nh, 128, generator=g).to(torch.bfloat16)
+        q = torch.randn(q_len, nh, 192, generator=g).to(torch.bfloat16)
+        q_pad = torch.zeros(kv_len, nh, 192, dtype=torch.bfloat16)
+        q_pad[kv_len - q_len:] = q
+        o = dense_causal_attention(q_pad, k, v, [kv_len], scale)[kv_len - q_len:]
+        rows.append(dict(q_len=q_len, kv_len=kv_len, q=q, k=k, v=v, o=o))
+    out["decode_rows"] = dict(nh=nh, scale=scale, rows=rows)
+    return out
+
+
 def wrapper_case():
     """Whole GQA sub-block through the reference's DenseBackend.attention
     (packed projection, RoPE, core, o_proj) on one prefill sequence, bf16."""
@@ -231,8 +319,12 @@ def _compact(obj):
 
 def main():
     torch.set_num_threads(1)
+    if "--mla-paged-only" in sys.argv:          # adds the newest file without touching the others
+        torch.save(_compact(mla_paged_cases()), os.path.join(HERE, "reference_mla_paged.pt"))
+        return
     small = dict(dense=dense_cases(), slots=slot_cases(), mla=mla_cases(), wrapper=wrapper_case())
     torch.save(_compact(small), os.path.join(HERE, "reference_small.pt"))
+    torch.save(_compact(mla_paged_cases()), os.path.join(HERE, "reference_mla_paged.pt"))
     torch.save(_compact(dict(paged=paged_cases())), os.path.join(HERE, "reference_paged.pt"))
     for name in ("reference_small.pt", "reference_paged.pt"):
         print(name, os.path.getsize(os.path.join(HERE, name)) // 1024, "KiB")
