@@ -142,6 +142,61 @@ def test_plan_modes_on_the_benchmark_shapes(lib):
     _check_cover(items, multi, c3, 1, 32, info)
 
 
+def _mha_plan(lib, cu, kv, heads, num_ctas, base=None):
+    from auto_infer_b200._lib import MhaPlanInfo
+    n = len(cu)
+    tokens = cu[-1] if cu else 0
+    nbytes = lib.b200_mha_plan_bytes(n, tokens, heads)
+    host = (ctypes.c_int32 * max(nbytes // 4, 16))()
+    cu_a, kv_a = (ctypes.c_int32 * max(n, 1))(*cu), (ctypes.c_int32 * max(n, 1))(*kv)
+    base_a = (ctypes.c_int32 * n)(*base) if base is not None else None
+    info = MhaPlanInfo()
+    rc = lib.b200_mha_plan(cu_a, kv_a, base_a, n, heads, num_ctas, host, nbytes, ctypes.byref(info))
+    assert rc == 0, lib.b200_last_error()
+    items = [tuple(host[16 + 12 * i + k] for k in range(9)) for i in range(info.num_items)]
+    return info, list(host[:16]), items
+
+
+def test_mha_plan_covers_every_row_and_key_once(lib):
+    """Blocks of 64 query positions per head; the tiles a block can see are dealt to the
+    splits without gap or overlap; long items come first."""
+    cu, kv, heads = [1, 131, 136, 136], [5000, 1000, 5, 77], 4
+    for num_ctas in (1, 148, 4000):
+        info, hdr, items = _mha_plan(lib, cu, kv, heads, num_ctas)
+        assert hdr[1] == info.num_items == len(items) and hdr[2] == info.num_splits and hdr[3] == 136
+        assert 1 <= info.num_splits <= 8
+        lengths = [it[5] - it[4] for it in items]
+        assert lengths == sorted(lengths, reverse=True)
+        seen = {}
+        for seq, head, tok0, n_rows, t0, t1, kv_len, limit0, split in items:
+            assert 0 < n_rows <= 64 and kv_len == kv[seq] and 0 <= t0 <= t1
+            seen.setdefault((tok0, head), []).append((split, t0, t1, seq, n_rows, limit0))
+        prev, blocks = 0, []
+        for b, end in enumerate(cu):
+            for r in range(0, end - prev, 64):
+                blocks.append((prev + r, b, min(64, end - prev - r), kv[b] - (end - prev) + r))
+            prev = end
+        assert len(seen) == len(blocks) * heads
+        for tok0, b, n_rows, limit0 in blocks:
+            for h in range(heads):
+                parts = sorted(seen[(tok0, h)])
+                assert [p[0] for p in parts] == list(range(info.num_splits))
+                assert all(p[3:] == (b, n_rows, limit0) for p in parts)
+                n_tiles = min(limit0 + n_rows - 1, kv[b] - 1) // 64 + 1
+                at = 0
+                for _, t0, t1, *_ in parts:
+                    assert t0 == min(at, n_tiles) and t1 >= t0
+                    at = t1
+                assert at == n_tiles
+        assert info.total_tiles == sum(lengths)
+    # one CTA wanted: no splits; many: the longest block is cut
+    assert _mha_plan(lib, cu, kv, heads, 1)[0].num_splits == 1
+    assert _mha_plan(lib, cu, kv, heads, 4000)[0].num_splits == 8
+    # an empty step is an empty plan
+    info, _, items = _mha_plan(lib, [], [], heads, 148)
+    assert info.num_items == 0 and not items
+
+
 def test_plan_rejects_bad_arguments(lib):
     import torch
     from auto_infer_b200._lib import DecodePlanInfo

@@ -73,6 +73,22 @@ def test_mla_family_caches_the_latent_once():
     assert k_cache is v_cache and k_cache.shape == (4, 128, 1, 576)
 
 
+def test_mla_family_keeps_the_reference_per_head_caches_on_request():
+    """``_mla_b200_absorb = False``: the non-absorbed form with the cache shapes of
+    auto_infer/layers/attention/mla.py:214-216."""
+    from auto_infer_b200.mla import B200MlaPagedBackend
+    model = _mla_model()
+    model._mla_b200_absorb = False
+    backend, caches = registry.build_attention_backend(model, "paged", num_blocks=4, block_size=16)
+    assert isinstance(backend, B200MlaPagedBackend) and not backend.absorb
+    k_cache, v_cache = caches[0]
+    assert k_cache.shape == (4, 16, 16, 192) and v_cache.shape == (4, 16, 16, 128)
+    with pytest.raises(NotImplementedError):
+        B200MlaPagedBackend({}, num_heads=4, qk_nope=64, qk_rope=32, v_head_dim=64, kv_lora_rank=64,
+                            q_lora_rank=None, rms_eps=1e-6, softmax_scale=1.0, num_layers=1, device="cpu",
+                            dtype=torch.bfloat16)
+
+
 def test_registry_errors_match_the_reference():
     with pytest.raises(ValueError, match="unsupported attention mode"):
         registry.build_attention_backend(_gqa_model(), "eager")
