@@ -108,6 +108,10 @@ SIGNATURES = {
         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "b200_copy_blocks": (c_int, [
         c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "b200_mla_decode_absorbed_replayable": (c_int, [
+        c_void_p, c_int64, c_void_p, c_int, c_int, c_void_p, c_int64,
+        c_void_p, c_int, c_int, c_int, c_int, c_float,
+        c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_lse_combine": (c_int, [
         c_void_p, c_void_p, c_int64, c_int64, c_int, c_int64, c_int,
         c_void_p, c_int, c_void_p, c_void_p]),

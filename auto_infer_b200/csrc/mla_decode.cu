@@ -19,6 +19,8 @@
 //     its 128 of the 512 value dims with P straight from registers;
 //   * the groups' (m, l, O) are merged in a fixed order at the end of an item.
 // Algorithmic bytes per launch: sum_b kv_len_b * 1 152 B (+ q, o).
+#include <algorithm>
+
 #include "common.cuh"
 #include "decode_plan.h"
 #include "split_merge.cuh"
@@ -66,6 +68,7 @@ struct MlaParams {
   float* lse_out;
   int32_t* status;
   int num_heads;
+  int max_partials;                // records the workspace holds
   int block_size, block_shift, num_blocks, box_tokens, boxes_per_tile;
   int out_is_f32;
   float scale, scale_log2;
@@ -125,6 +128,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   __syncthreads();
   grid_dep_launch();              // the merge kernel may be scheduled; it waits for this grid itself
   grid_dep_wait();                // q and the step's new latent rows come from earlier kernels
+  if (plan[kHdrMagic] != kPlanMagic || plan[kHdrNumCtas] != (int)gridDim.x) {   // not a plan for this launch
+    if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200_STATUS_BAD_LAUNCH);
+    return;
+  }
   if (item_begin >= item_end) return;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -416,7 +423,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
       }
     }
     named_bar_sync(3, kMlaConsumerThreads);
-    if (grp == 0) {
+    const bool record_fits = item.direct || item.partial_idx < p.max_partials;
+    if (!record_fits && threadIdx.x == 0 && p.status)
+      atomicOr(p.status, B200_STATUS_BAD_LAUNCH);              // workspace smaller than the plan needs
+    if (grp == 0 && record_fits) {
       const float* slot = sm.slots[gw];
       // row sums over both groups
       float ls0 = 0.f, ls1 = 0.f;
@@ -486,48 +496,55 @@ static long long* g_mla_trace = nullptr;
 extern "C" void b200_debug_set_mla_trace(void* dev_ptr) { g_mla_trace = static_cast<long long*>(dev_ptr); }
 #endif
 
-extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
-                                        const void* latent_cache, int num_blocks, int block_size,
-                                        const int32_t* block_table, int64_t bt_stride,
-                                        const int32_t* plan_dev, const b200_decode_plan_info* info,
-                                        int num_heads, int kv_lora_rank, int rope_dim, float scale,
-                                        void* workspace, size_t workspace_bytes, void* out,
-                                        int out_is_f32, float* lse_out, int32_t* status,
-                                        void* stream) {
-  using namespace b200;
-  if (!info) {
-    set_last_error("mla_decode_absorbed: plan info is null");
-    return B200_EINVAL;
-  }
-  if (info->num_items == 0) return B200_OK;
+namespace b200 {
+
+// `info` given: the launch is sized by the plan (its CTAs, its partial records, its cut pairs).
+// `info` null: the replayable form - grid num_ctas, the workspace cut for as many records as it
+// holds, the merge launched for the most cut pairs a plan of num_ctas CTAs can have; counts and
+// offsets are read from the plan on the device.
+static int launch_mla(const char* who, const void* q_latent, int64_t q_stride, const void* latent_cache,
+                      int num_blocks, int block_size, const int32_t* block_table, int64_t bt_stride,
+                      const int32_t* plan_dev, const b200_decode_plan_info* info, int num_ctas, int num_heads,
+                      int kv_lora_rank, int rope_dim, float scale, void* workspace, size_t workspace_bytes,
+                      void* out, int out_is_f32, float* lse_out, int32_t* status, void* stream) {
   if (!q_latent || !latent_cache || !block_table || !plan_dev || !out || !workspace ||
-      num_blocks <= 0 || num_heads <= 0) {
-    set_last_error("mla_decode_absorbed: null pointer or non-positive size");
+      num_blocks <= 0 || num_heads <= 0 || num_ctas <= 0) {
+    set_last_error("%s: null pointer or non-positive size", who);
     return B200_EINVAL;
   }
   if (kv_lora_rank != kValueDim || rope_dim != kLatentDim - kValueDim) {
-    set_last_error("mla_decode_absorbed: latent %d+%d unsupported (kernel is built for 512+64)",
-                   kv_lora_rank, rope_dim);
+    set_last_error("%s: latent %d+%d unsupported (kernel is built for 512+64)", who, kv_lora_rank, rope_dim);
     return B200_EUNSUPPORTED;
   }
   if (num_heads > kMaxRows) {
-    set_last_error("mla_decode_absorbed: %d heads exceed the 16 query rows of one MMA tile", num_heads);
+    set_last_error("%s: %d heads exceed the 16 query rows of one MMA tile", who, num_heads);
     return B200_EUNSUPPORTED;
   }
   if (block_size < 8 || (block_size & (block_size - 1))) {
-    set_last_error("mla_decode_absorbed: block_size %d must be a power of two >= 8", block_size);
+    set_last_error("%s: block_size %d must be a power of two >= 8", who, block_size);
     return B200_EUNSUPPORTED;
   }
   if (reinterpret_cast<uintptr_t>(q_latent) % 16 || (q_stride % 8) ||
       q_stride < (int64_t)num_heads * kLatentDim || reinterpret_cast<uintptr_t>(out) % 16 ||
       reinterpret_cast<uintptr_t>(workspace) % 16) {
-    set_last_error("mla_decode_absorbed: q, out and workspace must be 16-byte aligned, q stride a multiple of 8");
+    set_last_error("%s: q, out and workspace must be 16-byte aligned, q stride a multiple of 8", who);
     return B200_EALIGN;
   }
-  const size_t need = (size_t)info->num_partials * (kMaxRows * (size_t)kValueDim + kMaxRows) * sizeof(float);
-  if (workspace_bytes < need) {
-    set_last_error("mla_decode_absorbed: workspace %zu bytes < %zu needed", workspace_bytes, need);
-    return B200_EPLAN;
+  const size_t record_bytes = (kMaxRows * (size_t)kValueDim + kMaxRows) * sizeof(float);
+  int max_partials;
+  if (info) {
+    max_partials = info->num_partials;
+    if (workspace_bytes < (size_t)max_partials * record_bytes) {
+      set_last_error("%s: workspace %zu bytes < %zu needed", who, workspace_bytes, (size_t)max_partials * record_bytes);
+      return B200_EPLAN;
+    }
+  } else {
+    max_partials = (int)std::min<size_t>(workspace_bytes / record_bytes, (size_t)1 << 24);
+    if (max_partials < num_ctas) {
+      set_last_error("%s: workspace %zu bytes holds fewer than num_ctas = %d records; size it with "
+                     "b200_mla_decode_workspace_bytes", who, workspace_bytes, num_ctas);
+      return B200_EPLAN;
+    }
   }
   const int box_tokens = block_size < kMlaTileTokens ? block_size : kMlaTileTokens;
   CUtensorMap lat_map;
@@ -541,11 +558,12 @@ extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
   p.bt_stride = bt_stride;
   p.plan = plan_dev;
   p.part_o = static_cast<float*>(workspace);
-  p.part_lse = p.part_o + (size_t)info->num_partials * kMaxRows * kValueDim;
+  p.part_lse = p.part_o + (size_t)max_partials * kMaxRows * kValueDim;
   p.out = out;
   p.lse_out = lse_out;
   p.status = status;
   p.num_heads = num_heads;
+  p.max_partials = max_partials;
   p.block_size = block_size;
   p.block_shift = __builtin_ctz(block_size);
   p.num_blocks = num_blocks;
@@ -570,14 +588,50 @@ extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
     if (rc) return rc;
     if (dev < 64) attr_set[dev] = true;
   }
-  rc = check_cuda(launch_pdl(mla_decode_kernel, dim3(info->num_ctas), dim3(kMlaThreads), smem, s, lat_map, p),
+  rc = check_cuda(launch_pdl(mla_decode_kernel, dim3(num_ctas), dim3(kMlaThreads), smem, s, lat_map, p),
                   "mla_decode launch");
   if (rc) return rc;
-  if (info->num_multi > 0) {
-    rc = check_cuda(launch_pdl(split_merge_kernel<kValueDim>, dim3(split_merge_grid<kValueDim>(info->num_multi)),
+  const int merge_pairs = info ? info->num_multi : num_ctas;     // a plan of n CTAs cuts at most n pairs
+  if (merge_pairs > 0) {
+    rc = check_cuda(launch_pdl(split_merge_kernel<kValueDim>, dim3(split_merge_grid<kValueDim>(merge_pairs)),
                                dim3(128), 0, s, plan_dev, (const float*)p.part_o, (const float*)p.part_lse,
                                out, lse_out, num_heads, num_heads, out_is_f32),
                     "mla_merge launch");
   }
   return rc;
+}
+
+}  // namespace b200
+
+extern "C" int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
+                                        const void* latent_cache, int num_blocks, int block_size,
+                                        const int32_t* block_table, int64_t bt_stride,
+                                        const int32_t* plan_dev, const b200_decode_plan_info* info,
+                                        int num_heads, int kv_lora_rank, int rope_dim, float scale,
+                                        void* workspace, size_t workspace_bytes, void* out,
+                                        int out_is_f32, float* lse_out, int32_t* status,
+                                        void* stream) {
+  using namespace b200;
+  if (!info) {
+    set_last_error("mla_decode_absorbed: plan info is null");
+    return B200_EINVAL;
+  }
+  if (info->num_items == 0) return B200_OK;
+  return launch_mla("mla_decode_absorbed", q_latent, q_stride, latent_cache, num_blocks, block_size, block_table,
+                    bt_stride, plan_dev, info, info->num_ctas, num_heads, kv_lora_rank, rope_dim, scale, workspace,
+                    workspace_bytes, out, out_is_f32, lse_out, status, stream);
+}
+
+extern "C" int b200_mla_decode_absorbed_replayable(const void* q_latent, int64_t q_stride,
+                                                   const void* latent_cache, int num_blocks, int block_size,
+                                                   const int32_t* block_table, int64_t bt_stride,
+                                                   const int32_t* plan_dev, int num_ctas, int num_heads,
+                                                   int kv_lora_rank, int rope_dim, float scale,
+                                                   void* workspace, size_t workspace_bytes, void* out,
+                                                   int out_is_f32, float* lse_out, int32_t* status,
+                                                   void* stream) {
+  using namespace b200;
+  return launch_mla("mla_decode_absorbed_replayable", q_latent, q_stride, latent_cache, num_blocks, block_size,
+                    block_table, bt_stride, plan_dev, nullptr, num_ctas, num_heads, kv_lora_rank, rope_dim, scale,
+                    workspace, workspace_bytes, out, out_is_f32, lse_out, status, stream);
 }

@@ -19,6 +19,8 @@ split_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ p
   constexpr int kRowsPerCta = 512 / kDim;            // 1 (MLA) or 4 (GQA)
   constexpr int kThreadsPerRow = kDim / 4;
   constexpr int kCtasPerPair = kMaxRows / kRowsPerCta;
+  // a replayable launch has the grid of the largest plan: CTAs past this plan's cut pairs leave
+  if ((int)(blockIdx.x / kCtasPerPair) >= plan[kHdrNumMulti]) return;
   const MultiGroup g = reinterpret_cast<const MultiGroup*>(plan + plan[kHdrOffMulti])[blockIdx.x / kCtasPerPair];
   const int rows = g.q_len * group;
   const int row = (blockIdx.x % kCtasPerPair) * kRowsPerCta + threadIdx.x / kThreadsPerRow;

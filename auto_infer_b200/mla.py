@@ -12,6 +12,9 @@ W_UV, then o_proj.  The two vendor calls in it (cache write, paged attention) go
 to the CUDA library; the latent is cached once per token instead of twice."""
 from __future__ import annotations
 
+from contextlib import nullcontext
+from dataclasses import dataclass
+
 import torch
 
 from . import ops
@@ -156,10 +159,123 @@ class B200MlaBackend(AttentionBackend):
             cu, kv = new_cu, new_kv
             block_table = block_table.index_select(
                 0, torch.tensor(rows, dtype=torch.long, device=block_table.device))
-        plan = ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank)
+        plan = self._make_plan(cu, kv, device, wide)
         assert plan.skipped_seqs == 0
         setattr(ctx, "_b200_mla_plan", ((self.num_heads, str(device)), plan, block_table))
         return plan, block_table
+
+    def _make_plan(self, cu, kv, device, wide: bool):
+        return ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank)
+
+
+@dataclass(frozen=True)
+class _GraphMlaRegistration:
+    """One captured latent-attention call: the refillable plan its launch reads and the static
+    tensors it was recorded against (the counterpart of ``_FiaRegistration``,
+    auto_infer/layers/attention/graph_fia.py:6-14)."""
+    plan: object
+    layer_idx: int
+    query: torch.Tensor
+    output: torch.Tensor
+
+
+class B200GraphMlaBackend(B200MlaBackend):
+    """Graph-capturable absorbed MLA: the lifecycle surface of ``GraphFiaLifecycle``
+    (auto_infer/layers/attention/graph_fia.py:17-104: ``capturing``, ``reg``,
+    ``begin_capture() / end_capture()``, ``update() / update_registrations() /
+    update_many()``) that the graph runners drive on ``GraphMlaBackend``
+    (auto_infer/layers/attention/mla.py:258-366), over the latent kernel.  The reference's
+    graph flavour of MLA is the non-absorbed one, because its vendor op cannot take the
+    576-wide head; here the captured launch is the absorbed kernel reading lengths and work
+    list from a plan at a fixed device address, and an update is one refill of that plan for
+    all layers.  Decode gears only (``supports_prefill_graph`` False): a prefill chunk is
+    planned as one single-token sequence per query row, whose count changes with the step.
+
+    Capture protocol as for ``B200GraphGqaBackend``: one eager step with the context the
+    capture will use (that allocates the plan), ``begin_capture()``, the same step recorded
+    with the same context object, ``end_capture()``, ``gear.reg = backend.reg``."""
+
+    supports_prefill_graph = False
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.capturing = False
+        self.reg: list = []
+        self._plan_pool: dict = {}        # refillable plans by batch size
+
+    def begin_capture(self) -> None:
+        self.capturing = True
+        self.reg = []
+
+    def end_capture(self) -> None:
+        self.capturing = False
+
+    def _make_plan(self, cu, kv, device, wide: bool):
+        if wide:        # per-row expansion: not replayable, and never recorded
+            return ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank)
+        key = (len(cu), str(device))
+        plan = self._plan_pool.get(key)
+        if plan is None:
+            if self.capturing:
+                raise RuntimeError(
+                    "capture needs one eager step with the same context first (capturing False): the "
+                    "plan's buffers cannot be allocated while the stream is being captured")
+            plan = ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank,
+                                     capacity_seqs=len(cu))
+            self._plan_pool[key] = plan
+        else:
+            plan.refill(cu, kv)
+        return plan
+
+    def _latent_attn(self, layer_idx: int, q_latent: torch.Tensor, ctx) -> torch.Tensor:
+        if not self.capturing:
+            return super()._latent_attn(layer_idx, q_latent, ctx)
+        cached = getattr(ctx, "_b200_mla_plan", None)
+        if cached is None or cached[0] != (self.num_heads, str(q_latent.device)) or not cached[1].replayable:
+            raise RuntimeError(
+                "capture needs one eager step with the same context first (capturing False), and a "
+                "decode-shaped step: a prefill chunk cannot be recorded")
+        plan, block_table = cached[1], cached[2]
+        for key, pooled in list(self._plan_pool.items()):
+            if pooled is plan:                      # the plan now belongs to this capture
+                del self._plan_pool[key]
+        latent_cache = ctx.kv_caches[layer_idx][0]
+        out = ops.mla_decode_absorbed(q_latent, latent_cache, block_table, plan, self.softmax_scale,
+                                      kv_lora_rank=self.kv_lora_rank)
+        self.reg.append(_GraphMlaRegistration(plan, layer_idx, q_latent, out))
+        return out
+
+    # -- per-step update (graph_fia.py:87-104) --------------------------------
+    def _refill(self, plan, ctx, stream) -> None:
+        cu, kv = list(ctx.cu_seqlens_q), list(ctx.seqlens_kv)
+        max_q = max(1, 16 // self.num_heads)
+        prev = 0
+        for end in cu:
+            if end - prev > max_q:
+                raise ValueError("this graph was captured on a decode-shaped step: a step with wider query "
+                                 "blocks runs eagerly")
+            prev = end
+        with (torch.cuda.stream(stream) if stream is not None else nullcontext()):
+            plan.refill(cu, kv)
+
+    def update(self, ctx, stream=None) -> None:
+        self.update_registrations(self.reg, ctx, stream)
+
+    def update_registrations(self, registrations, ctx, stream=None) -> None:
+        seen = set()
+        for registration in registrations:
+            if id(registration.plan) not in seen:
+                seen.add(id(registration.plan))
+                self._refill(registration.plan, ctx, stream)
+
+    def update_many(self, contexts, stream=None) -> None:
+        if len(contexts) != len(self.reg):
+            raise ValueError("graph-task contexts must match registrations")
+        seen = set()
+        for ctx, registration in zip(contexts, self.reg):
+            if id(registration.plan) not in seen:
+                seen.add(id(registration.plan))
+                self._refill(registration.plan, ctx, stream)
 
 
 def ds_rope_interleave(x: torch.Tensor) -> torch.Tensor:

@@ -151,15 +151,24 @@ class DecodePlan:
         used = max(int(self.info.plan_ints), 16)
         if self.replayable:
             self.dev = torch.zeros(self._nbytes // 4, dtype=torch.int32, device=self.device)
-            ws = lib.b200_decode_workspace_bytes(self.capacity_seqs, num_kv_heads, self.num_ctas, head_dim)
+            ws = self._capacity_workspace_bytes()
         else:
             self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
             ws = (self.info.num_partials * (16 * head_dim + 16)) * 4 + 256
         self._upload(used)
         self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
 
+    def _capacity_workspace_bytes(self) -> int:
+        return _lib.load().b200_decode_workspace_bytes(self.capacity_seqs, self.num_kv_heads, self.num_ctas,
+                                                       self.head_dim)
+
+    def _call_planner(self, cu, kv, base) -> None:
+        rc = _lib.load().b200_decode_plan(cu, kv, base, self.num_seqs,
+                                          self.num_q_heads, self.num_kv_heads, self.num_ctas,
+                                          self.host.data_ptr(), self._nbytes, ctypes.byref(self.info))
+        _lib.check(rc, "b200_decode_plan")
+
     def _build(self, cu_seqlens_q, seqlens_kv, causal_base) -> None:
-        lib = _lib.load()
         self.num_seqs = len(cu_seqlens_q)
         if self.num_seqs > self.capacity_seqs:
             raise ValueError(f"{self.num_seqs} sequences exceed the plan's capacity of {self.capacity_seqs}")
@@ -168,10 +177,7 @@ class DecodePlan:
         cu = int_array(*cu_seqlens_q)
         kv = int_array(*seqlens_kv)
         base = int_array(*causal_base) if causal_base is not None else None
-        rc = lib.b200_decode_plan(cu, kv, base, self.num_seqs,
-                                  self.num_q_heads, self.num_kv_heads, self.num_ctas,
-                                  self.host.data_ptr(), self._nbytes, ctypes.byref(self.info))
-        _lib.check(rc, "b200_decode_plan")
+        self._call_planner(cu, kv, base)
 
     def _upload(self, used: int) -> None:
         self.dev[:used].copy_(self.host[:used], non_blocking=True)
@@ -294,42 +300,25 @@ def paged_decode_gqa_write(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
     return out
 
 
-class MlaDecodePlan:
-    """Host plan + device copy + workspace of the absorbed-MLA decode kernel
-    (32-token latent tiles, one shared latent head)."""
+class MlaDecodePlan(DecodePlan):
+    """Host plan + device copy + workspace of the absorbed-MLA decode kernel (32-token latent
+    tiles, one shared latent head).  ``capacity_seqs`` makes it replayable like ``DecodePlan``:
+    fixed addresses, ``refill()`` in place, a launch that depends on ``num_ctas`` only."""
 
     def __init__(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int], num_heads: int,
                  device, kv_lora_rank: int = 512, num_ctas: Optional[int] = None,
-                 causal_base: Optional[Sequence[int]] = None):
-        lib = _lib.load()
-        self.device = torch.device(device)
-        if self.device.type != "cuda":
-            raise RuntimeError("MlaDecodePlan needs a CUDA device (no CPU fallback)")
-        num_seqs = len(cu_seqlens_q)
+                 causal_base: Optional[Sequence[int]] = None, capacity_seqs: Optional[int] = None):
         self.num_heads = num_heads
-        self.num_ctas = int(num_ctas) if num_ctas else sm_count(self.device)
-        nbytes = lib.b200_decode_plan_bytes(num_seqs, 1, self.num_ctas)
-        self.host = torch.empty(nbytes // 4, dtype=torch.int32, pin_memory=True)
-        cu = torch.tensor(list(cu_seqlens_q), dtype=torch.int32)
-        kv = torch.tensor(list(seqlens_kv), dtype=torch.int32)
-        base_ptr = None
-        if causal_base is not None:
-            base = torch.tensor(list(causal_base), dtype=torch.int32)
-            base_ptr = base.data_ptr()
-        self.info = DecodePlanInfo()
-        rc = lib.b200_mla_decode_plan(cu.data_ptr(), kv.data_ptr(), base_ptr, num_seqs, num_heads,
-                                      self.num_ctas, self.host.data_ptr(), nbytes,
-                                      ctypes.byref(self.info))
-        _lib.check(rc, "b200_mla_decode_plan")
-        used = max(int(self.info.plan_ints), 16)
-        self.dev = torch.empty(used, dtype=torch.int32, device=self.device)
-        self.dev.copy_(self.host[:used], non_blocking=True)
-        ws = (self.info.num_partials * (16 * kv_lora_rank + 16)) * 4 + 256
-        self.workspace = torch.empty(ws, dtype=torch.uint8, device=self.device)
+        super().__init__(cu_seqlens_q, seqlens_kv, num_heads, 1, device, head_dim=kv_lora_rank,
+                         num_ctas=num_ctas, causal_base=causal_base, capacity_seqs=capacity_seqs)
 
-    @property
-    def skipped_seqs(self) -> int:
-        return int(self.info.skipped_seqs)
+    def _capacity_workspace_bytes(self) -> int:
+        return _lib.load().b200_mla_decode_workspace_bytes(self.capacity_seqs, self.num_ctas, self.head_dim)
+
+    def _call_planner(self, cu, kv, base) -> None:
+        rc = _lib.load().b200_mla_decode_plan(cu, kv, base, self.num_seqs, self.num_heads, self.num_ctas,
+                                              self.host.data_ptr(), self._nbytes, ctypes.byref(self.info))
+        _lib.check(rc, "b200_mla_decode_plan")
 
 
 def mla_decode_absorbed(q_latent: torch.Tensor, latent_cache: torch.Tensor,
@@ -354,15 +343,21 @@ def mla_decode_absorbed(q_latent: torch.Tensor, latent_cache: torch.Tensor,
     if out is None:
         out = torch.empty(t, h, kv_lora_rank, dtype=torch.float32 if out_f32 else q_latent.dtype,
                           device=q_latent.device)
-    with _on_device(q_latent.device):
-        rc = lib.b200_mla_decode_absorbed(
-            q_latent.data_ptr(), q_latent.stride(0), latent_cache.data_ptr(), num_blocks, block_size,
-            block_table.data_ptr(), block_table.stride(0), plan.dev.data_ptr(),
-            ctypes.byref(plan.info), h, kv_lora_rank, width - kv_lora_rank, float(scale),
+    tail = (h, kv_lora_rank, width - kv_lora_rank, float(scale),
             plan.workspace.data_ptr(), plan.workspace.numel(), out.data_ptr(),
             1 if out.dtype == torch.float32 else 0,
             lse_out.data_ptr() if lse_out is not None else None,
             status_word(q_latent.device).data_ptr(), _stream_ptr(q_latent.device))
+    with _on_device(q_latent.device):
+        if plan.replayable:
+            rc = lib.b200_mla_decode_absorbed_replayable(
+                q_latent.data_ptr(), q_latent.stride(0), latent_cache.data_ptr(), num_blocks, block_size,
+                block_table.data_ptr(), block_table.stride(0), plan.dev.data_ptr(), plan.num_ctas, *tail)
+        else:
+            rc = lib.b200_mla_decode_absorbed(
+                q_latent.data_ptr(), q_latent.stride(0), latent_cache.data_ptr(), num_blocks, block_size,
+                block_table.data_ptr(), block_table.stride(0), plan.dev.data_ptr(), ctypes.byref(plan.info),
+                *tail)
     _lib.check(rc, "b200_mla_decode_absorbed")
     return out
 

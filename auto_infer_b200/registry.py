@@ -63,7 +63,7 @@ def _gqa_mtp(model, mode: str, prefix: str):
 
 
 def _mla(model, mode: str):
-    from .mla import B200MlaBackend, B200MlaPagedBackend
+    from .mla import B200GraphMlaBackend, B200MlaBackend, B200MlaPagedBackend
     if mode == "dense":
         _dense_unavailable("mla")
     cfg = model.cfg
@@ -72,7 +72,12 @@ def _mla(model, mode: str):
     # that sets ``_mla_b200_absorb = False`` keeps the reference's per-head K 192 / V 128
     # caches (auto_infer/layers/attention/registry.py:80-85 reads ``_mla_absorb`` the same way).
     absorb = getattr(model, "_mla_b200_absorb", True)
-    cls = B200MlaBackend if absorb else B200MlaPagedBackend
+    if mode == "graph":
+        if not absorb:
+            raise NotImplementedError("mla: mode 'graph' is built for the absorbed form only")
+        cls = B200GraphMlaBackend
+    else:
+        cls = B200MlaBackend if absorb else B200MlaPagedBackend
     return cls(
         model.w, num_heads=cfg.num_heads, qk_nope=cfg.qk_nope, qk_rope=cfg.qk_rope,
         v_head_dim=cfg.v_head_dim, kv_lora_rank=cfg.kv_lora_rank, q_lora_rank=cfg.q_lora_rank,

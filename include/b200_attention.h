@@ -339,6 +339,25 @@ int b200_mla_decode_absorbed(const void* q_latent, int64_t q_stride,
                              void* out, int out_is_f32, float* lse_out,
                              int32_t* status, void* stream);
 
+/* The same attention as a launch that can be recorded once and replayed for other
+ * steps (CUDA graph), as b200_paged_decode_gqa_replayable: the grid is num_ctas,
+ * counts and offsets are read from plan_dev; plan_dev has
+ * b200_decode_plan_bytes(num_seqs, 1, num_ctas) bytes and the workspace
+ * b200_mla_decode_workspace_bytes(num_seqs, num_ctas, 512) bytes for the largest
+ * step the recording has to serve; before each replay the caller copies the new
+ * plan to the same address.  The merge of cut sequences is launched for the most
+ * cut sequences such a plan can have and leaves early for the rest.  A plan built
+ * for another num_ctas, or one that needs more records than the workspace holds,
+ * sets B200_STATUS_BAD_LAUNCH. */
+int b200_mla_decode_absorbed_replayable(const void* q_latent, int64_t q_stride,
+                                        const void* latent_cache, int num_blocks, int block_size,
+                                        const int32_t* block_table, int64_t bt_stride,
+                                        const int32_t* plan_dev, int num_ctas,
+                                        int num_heads, int kv_lora_rank, int rope_dim, float scale,
+                                        void* workspace, size_t workspace_bytes,
+                                        void* out, int out_is_f32, float* lse_out,
+                                        int32_t* status, void* stream);
+
 /* ------------------------------------------------------------------------ *
  * Paged attention of the non-absorbed MLA form: one decompressed K (192 wide,
  * [k_nope | k_pe]) and V (128 wide) row per head and token, every query head

@@ -214,3 +214,100 @@ def test_capture_without_a_warm_up_step_is_refused():
     with pytest.raises(RuntimeError, match="one eager step with the same context first"):
         backend._attn(0, q, None, None, ctx)
     backend.end_capture()
+
+
+def test_mla_decode_gear_replays_for_other_lengths():
+    """The absorbed-MLA family in mode "graph": latent write + latent attention of a decode
+    gear recorded once, replayed after ``update_registrations`` for other length sets
+    (sequences cut over several CTAs included), every replay against the oracle."""
+    from auto_infer_b200 import ops, registry
+    from auto_infer_b200.forward_context import ForwardContext
+    from auto_infer_b200.mla import B200GraphMlaBackend
+    dev = torch.device("cuda")
+    heads, bs, gear, max_blocks, pool = 16, 16, 4, 80, 200
+    cfg = SimpleNamespace(num_heads=heads, qk_nope=128, qk_rope=64, v_head_dim=128, kv_lora_rank=512,
+                          q_lora_rank=None, rms_eps=1e-6, num_layers=2)
+    model = SimpleNamespace(cfg=cfg, w={}, layer_prefix=lambda i: f"model.layers.{i}.", device=dev,
+                            dtype=torch.bfloat16, _softmax_scale=192 ** -0.5, _mla_absorb=False,
+                            ATTENTION_FAMILY="mla")
+    backend, caches = registry.build_attention_backend(model, "graph", pool + gear, bs)
+    assert isinstance(backend, B200GraphMlaBackend) and not backend.supports_prefill_graph
+    g = torch.Generator().manual_seed(77)
+    for latent, _ in caches:
+        latent.copy_(torch.randn(latent.shape, generator=g).to(torch.bfloat16))
+
+    q = torch.zeros(gear, heads, 576, dtype=torch.bfloat16, device=dev)
+    k_new = torch.zeros(gear, 1, 576, dtype=torch.bfloat16, device=dev)
+    slots = torch.zeros(gear, dtype=torch.int32, device=dev)
+    block_table = torch.zeros(gear, max_blocks, dtype=torch.int32, device=dev)
+    cu_q = list(range(1, gear + 1))
+
+    def stage(requests):
+        s, kv = [], []
+        bt = torch.zeros(gear, max_blocks, dtype=torch.int32)
+        for row, (pos, blocks) in enumerate(requests):
+            s.append(blocks[pos // bs] * bs + pos % bs)
+            bt[row, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+            kv.append(pos + 1)
+        for row in range(len(requests), gear):                 # padding rows on scratch blocks
+            s.append((pool + row) * bs)
+            bt[row, 0] = pool + row
+            kv.append(1)
+        return torch.tensor(s, dtype=torch.int32), bt, kv
+
+    def ctx_for(kv_lens):
+        return ForwardContext(None, None, slots, block_table, cu_q, kv_lens, None, backend, caches, True)
+
+    def step(ctx):
+        return [backend.latent_attention(layer, q, k_new, ctx) for layer in range(cfg.num_layers)]
+
+    s0, bt0, kv0 = stage([])
+    slots.copy_(s0)
+    block_table.copy_(bt0)
+    ctx = ctx_for(kv0)
+    with pytest.raises(RuntimeError):                           # no warm-up step yet
+        backend.begin_capture()
+        try:
+            step(ctx_for(kv0))
+        finally:
+            backend.end_capture()
+    step(ctx)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    backend.begin_capture()
+    with torch.cuda.graph(graph):
+        outs = step(ctx)
+    backend.end_capture()
+    gear_reg = backend.reg
+    assert len(gear_reg) == cfg.num_layers and gear_reg[0].plan is gear_reg[1].plan
+
+    perm = torch.randperm(pool, generator=g).tolist()
+    length_sets = [
+        [(5, perm[0:1]), (40, perm[1:4])],
+        [(0, perm[4:5]), (1200, perm[5:81]), (63, perm[81:85]), (16, perm[85:87])],
+        [(bs * max_blocks - 1, perm[87:87 + max_blocks])],
+    ]
+    for requests in length_sets:
+        s_h, bt_h, kv_lens = stage(requests)
+        q_h = torch.randn(gear, heads, 576, generator=g).to(torch.bfloat16)
+        k_h = torch.randn(gear, 1, 576, generator=g).to(torch.bfloat16)
+        for dst, src in ((q, q_h), (k_new, k_h), (slots, s_h), (block_table, bt_h)):
+            dst.copy_(src)
+        ref_caches = [latent.cpu().clone() for latent, _ in caches]
+        # an eager step of another batch size in between must not disturb the captured plan
+        other = ForwardContext(None, None, slots[:1], block_table[:1], [1], [kv_lens[0]], None, backend, caches, True)
+        backend._latent_attn(0, q[:1], other)
+        backend.update_registrations(gear_reg, ctx_for(kv_lens))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ops.read_status(dev) == 0
+        live = len(requests)
+        for layer in range(cfg.num_layers):
+            lat = ref_caches[layer]
+            orc.write_kv(k_h, None, lat, None, s_h.tolist())
+            assert torch.equal(caches[layer][0].cpu(), lat)
+            ref, _ = orc.paged_attention(q_h, lat, lat, bt_h, cu_q, kv_lens, 192 ** -0.5, return_lse=True)
+            assert_attention_close(outs[layer].cpu()[:live], ref[:live, :, :512], what=f"layer {layer}")
+    with pytest.raises(ValueError):                             # a wider query block needs an eager step
+        backend.update_registrations(gear_reg, ForwardContext(None, None, slots, block_table, [2, 3, 4, 5],
+                                                              [9, 9, 9, 9], None, backend, caches, False))

@@ -89,6 +89,27 @@ def test_mla_family_keeps_the_reference_per_head_caches_on_request():
                             dtype=torch.bfloat16)
 
 
+def test_mla_graph_mode_has_the_lifecycle_surface():
+    """Mode "graph" of the MLA family: the attributes the graph runners touch
+    (auto_infer/layers/attention/graph_fia.py:17-104)."""
+    from auto_infer_b200.mla import B200GraphMlaBackend
+    backend, caches = registry.build_attention_backend(_mla_model(), "graph", num_blocks=4, block_size=128)
+    assert isinstance(backend, B200GraphMlaBackend) and caches[0][0].shape == (4, 128, 1, 576)
+    assert backend.capturing is False and backend.reg == [] and backend.supports_prefill_graph is False
+    backend.begin_capture()
+    assert backend.capturing and backend.reg == []
+    backend.end_capture()
+    assert not backend.capturing
+    for name in ("update", "update_registrations", "update_many"):
+        assert callable(getattr(backend, name))
+    with pytest.raises(ValueError):
+        backend.update_many([object()])
+    model = _mla_model()
+    model._mla_b200_absorb = False
+    with pytest.raises(NotImplementedError):
+        registry.build_attention_backend(model, "graph", num_blocks=4, block_size=128)
+
+
 def test_registry_errors_match_the_reference():
     with pytest.raises(ValueError, match="unsupported attention mode"):
         registry.build_attention_backend(_gqa_model(), "eager")
