@@ -82,8 +82,14 @@ struct MlaParams {
   do {                                                                                           \
     if (p.trace && blockIdx.x == 0 && lane == 0 && (tileno) < 64) p.trace[(tileno) * 8 + (slot)] = clock64(); \
   } while (0)
+// per-CTA time stamps (ns): entry, dependency met, first / last tile consumed, end; tiles, items
+#define MLA_CTA_TRACE(slot, value)                                                               \
+  do {                                                                                           \
+    if (p.trace && threadIdx.x == 0) p.trace[4096 + blockIdx.x * 8 + (slot)] = (long long)(value); \
+  } while (0)
 #else
 #define MLA_TRACE(slot, tileno) do {} while (0)
+#define MLA_CTA_TRACE(slot, value) do {} while (0)
 #endif
 
 struct MlaWalker {
@@ -126,8 +132,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
     mbar_fence_init();
   }
   __syncthreads();
+  MLA_CTA_TRACE(0, global_timer_ns());
   grid_dep_launch();              // the merge kernel may be scheduled; it waits for this grid itself
   grid_dep_wait();                // q and the step's new latent rows come from earlier kernels
+  MLA_CTA_TRACE(1, global_timer_ns());
   if (plan[kHdrMagic] != kPlanMagic || plan[kHdrNumCtas] != (int)gridDim.x) {   // not a plan for this launch
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200_STATUS_BAD_LAUNCH);
     return;
@@ -387,6 +395,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
       __syncwarp();
       if (lane == 0) mbar_arrive(&sm.empty[s]);
       if (gw == 0) MLA_TRACE(5, it);
+#ifdef B200_TRACE
+      if (it == 0) MLA_CTA_TRACE(2, global_timer_ns());
+      if (grp == 0) MLA_CTA_TRACE(3, global_timer_ns());
+      if (grp == 0) MLA_CTA_TRACE(5, it + 1);
+#endif
     }
 
     // ---- merge the two groups in a fixed order, write the item's result
@@ -484,6 +497,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
     // reading qbuf / slots of this item by then (all reads precede a barrier above
     // or belong to warps that must reach the next barrier themselves)
     named_bar_sync(3, kMlaConsumerThreads);
+    MLA_CTA_TRACE(4, global_timer_ns());
+    MLA_CTA_TRACE(6, w.item - item_begin + 1);
     ++w.item;
     w.load();
   }
