@@ -112,6 +112,12 @@ constexpr int kTcEpilogueThreads = 128;
 constexpr int kTcThreads = kTcSoftmaxThreads + 128 + kTcEpilogueThreads;   // whole warpgroups: 512 = 4 x 128
 // registers per thread after the hand-over below: 256 * 200 + 128 * 40 + 128 * 72 = 512 * 128
 constexpr int kTcRegsSoftmax = 200;
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 constexpr int kTcRegsOther = 40;
 constexpr int kTcRegsEpilogue = 72;
 constexpr int kTcTmemCols = 512;          // S0 [0,128) S1 [128,256) O [256,384) P_A [384,448) P_B [448,512)
@@ -487,15 +493,23 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
             for (int c = 0; c < 32; ++c)
               if (tbase + q4 * 32 + c > lim) sv[q4][c] = __float_as_uint(-INFINITY);
         }
+        // The softmax warps are bound by instruction issue (two of them share a scheduler):
+        // three-input maxima and, below, packed two-element fp32 multiply-adds and adds halve
+        // the count of the row maximum, the scaling and the row sum.
         float mx;
         {
           float mq[8];                      // eight independent chains instead of one of 128
 #pragma unroll
           for (int u = 0; u < 8; ++u) mq[u] = __uint_as_float(sv[0][u]);
 #pragma unroll
-          for (int c = 8; c < 128; ++c) mq[c & 7] = fmaxf(mq[c & 7], __uint_as_float(sv[c >> 5][c & 31]));
-          mx = fmaxf(fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])),
-                     fmaxf(fmaxf(mq[4], mq[5]), fmaxf(mq[6], mq[7])));
+          for (int c = 8; c < 120; c += 16)
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+              mq[u] = fmax3(mq[u], __uint_as_float(sv[(c + u) >> 5][(c + u) & 31]),
+                            __uint_as_float(sv[(c + 8 + u) >> 5][(c + 8 + u) & 31]));
+#pragma unroll
+          for (int u = 0; u < 8; ++u) mq[u] = fmaxf(mq[u], __uint_as_float(sv[3][24 + u]));
+          mx = fmaxf(fmax3(mq[0], mq[1], mq[2]), fmax3(fmax3(mq[3], mq[4], mq[5]), mq[6], mq[7]));
         }
         // the maximum O is scaled to after the previous tile (owned by the other group)
         float m_in = -INFINITY;
@@ -540,26 +554,32 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap k_map,
         // Probabilities, software-pipelined by a quarter of the row: the exponentials of
         // quarter q are issued while quarter q - 1 is summed and packed, so nothing waits for a
         // MUFU result.  P (bf16 pairs) goes to the group's buffer 64 columns at a time.
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        float2 ls[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), shift2 = make_float2(-ms, -ms);
         uint32_t pk[32];
 #pragma unroll
         for (int q4 = 0; q4 <= 4; ++q4) {
 #pragma unroll
           for (int c = 0; c < 32; c += 2) {
             if (q4 < 4) {
-              sv[q4][c] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sv[q4][c]), p.scale_log2, -ms)));
-              sv[q4][c + 1] = __float_as_uint(fast_exp2(fmaf(__uint_as_float(sv[q4][c + 1]), p.scale_log2, -ms)));
+              const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[q4][c]), __uint_as_float(sv[q4][c + 1])),
+                                          scale2, shift2);
+              sv[q4][c] = __float_as_uint(fast_exp2(x.x));
+              sv[q4][c + 1] = __float_as_uint(fast_exp2(x.y));
             }
             if (q4 > 0) {
-              const float p0 = __uint_as_float(sv[q4 - 1][c]), p1 = __uint_as_float(sv[q4 - 1][c + 1]);
-              ls[(c >> 1) & 3] += p0 + p1;
-              pk[((q4 - 1) & 1) * 16 + (c >> 1)] = pack_bf16(p0, p1);
+              const float2 pp = make_float2(__uint_as_float(sv[q4 - 1][c]), __uint_as_float(sv[q4 - 1][c + 1]));
+              ls[(c >> 1) & 3] = __fadd2_rn(ls[(c >> 1) & 3], pp);
+              pk[((q4 - 1) & 1) * 16 + (c >> 1)] = pack_bf16(pp.x, pp.y);
             }
           }
           if (q4 == 2) tmem_st32(p_col, pk);
           if (q4 == 4) tmem_st32(p_col + 32, pk);
         }
-        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        {
+          const float2 a = __fadd2_rn(ls[0], ls[1]), b = __fadd2_rn(ls[2], ls[3]);
+          l += (a.x + a.y) + (b.x + b.y);
+        }
         if (r == 0) PF_TRACE(2, it);
         tmem_wait_st();
         tc_fence_before();
