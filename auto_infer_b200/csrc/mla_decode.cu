@@ -122,6 +122,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   const DecodeItem* items = reinterpret_cast<const DecodeItem*>(plan + plan[kHdrOffItems]);
   const int item_begin = cta_rec->item_begin;
   const int item_end = cta_rec->item_end;
+  // read ahead of the dependency wait like the rest of the plan: it reaches the device by a copy,
+  // never by the kernel in front
+  const bool plan_ok = plan[kHdrMagic] == kPlanMagic && plan[kHdrNumCtas] == (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
@@ -136,7 +139,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   grid_dep_launch();              // the merge kernel may be scheduled; it waits for this grid itself
   grid_dep_wait();                // q and the step's new latent rows come from earlier kernels
   MLA_CTA_TRACE(1, global_timer_ns());
-  if (plan[kHdrMagic] != kPlanMagic || plan[kHdrNumCtas] != (int)gridDim.x) {   // not a plan for this launch
+  if (!plan_ok) {                 // not a plan for this launch
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, B200_STATUS_BAD_LAUNCH);
     return;
   }
