@@ -32,7 +32,7 @@ class PrefillPlanInfo(ctypes.Structure):
 class MhaPlanInfo(ctypes.Structure):
     """Mirror of ``b200_mha_plan_info``."""
     _fields_ = [("num_items", c_int32), ("num_splits", c_int32), ("num_tokens", c_int32),
-                ("plan_ints", c_int32), ("total_tiles", c_int64)]
+                ("plan_ints", c_int32), ("narrow", c_int32), ("reserved", c_int32), ("total_tiles", c_int64)]
 
 
 # name -> (restype, argtypes); one entry per function the header declares

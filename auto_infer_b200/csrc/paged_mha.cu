@@ -4,14 +4,17 @@
 // kernel serves decode rows and prefill chunks of any q_len, bottom-right causal.
 //
 // A work item is one block of up to 64 query positions of one (sequence, head) pair and one
-// contiguous share ("split") of the 64-token KV tiles those positions can see.  One CTA per
-// item, two CTAs per SM:
+// contiguous share ("split") of the 64-token KV tiles those positions can see.  One CTA per item:
 //   * producer warp: per tile three K boxes and two V boxes (64 dims x 64 tokens, 128-byte
-//     swizzle) by TMA into a two-stage ring;
-//   * four consumer warps, 16 query rows each (a warp without rows only keeps the ring
-//     moving): S = Q K^T with mma.sync m16n8k16 (Q fragments in registers, K by ldmatrix),
-//     online softmax in fp32 (exp2 domain), O += P V with P straight from registers and V by
-//     ldmatrix.trans.
+//     swizzle) by TMA into a ring of 40 KB stages;
+//   * four consumer warps: S = Q K^T with mma.sync m16n8k16 (Q fragments in registers, K by
+//     ldmatrix), online softmax in fp32 (exp2 domain), O += P V with P straight from registers
+//     and V by ldmatrix.trans.
+// Two instantiations.  "Wide" (any step): every warp owns 16 query rows and all 64 tokens of a
+// tile (a warp without rows only keeps the ring moving), two stages, two CTAs per SM.  "Narrow"
+// (a step in which every block has at most 16 rows: decode, verify): HBM-bound, so one CTA per SM
+// with a five-stage ring (four tiles, 160 KB, in flight), all four warps on the same 16 rows and a
+// quarter of each tile's tokens each, their (m, l, O) merged through shared memory at the end.
 // With one split the rows are written as bf16 (or fp32) results; with more, every split writes
 // a normalised fp32 row and its log-sum-exp, and b200_lse_combine merges the splits in a fixed
 // order.  The host plan picks the number of splits so that a decode batch of a few sequences
@@ -31,7 +34,8 @@ constexpr int kMhaVSub = kMhaVDim / 64;
 constexpr int kMhaSubBytes = kMhaTile * 128;                  // [64 tokens][64 dims] bf16
 constexpr int kMhaKBytes = kMhaKSub * kMhaSubBytes;
 constexpr int kMhaStageBytes = (kMhaKSub + kMhaVSub) * kMhaSubBytes;   // 40 960
-constexpr int kMhaStages = 2;
+constexpr int kMhaWideStages = 2;
+constexpr int kMhaNarrowStages = 5;
 constexpr int kMhaWarps = 4;
 constexpr int kMhaConsumerThreads = kMhaWarps * 32;
 constexpr int kMhaThreads = kMhaConsumerThreads + 32;
@@ -49,10 +53,11 @@ struct MhaItem {
 };
 static_assert(sizeof(MhaItem) == kMhaItemInts * 4, "item layout");
 
+template <int kStages>
 struct __align__(1024) MhaSmem {
-  uint8_t stage[kMhaStages][kMhaStageBytes];
-  uint64_t full[kMhaStages];
-  uint64_t empty[kMhaStages];
+  uint8_t stage[kStages][kMhaStageBytes];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
   int abort_flag;
 };
 
@@ -73,11 +78,14 @@ struct MhaParams {
   float scale, scale_log2;
 };
 
-__global__ void __launch_bounds__(kMhaThreads, 2)
+template <bool kNarrow>
+__global__ void __launch_bounds__(kMhaThreads, kNarrow ? 1 : 2)
 paged_mha_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                  const MhaParams p) {
+  constexpr int kMhaStages = kNarrow ? kMhaNarrowStages : kMhaWideStages;
   extern __shared__ uint8_t smem_raw[];
-  MhaSmem& sm = *reinterpret_cast<MhaSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  MhaSmem<kMhaStages>& sm =
+      *reinterpret_cast<MhaSmem<kMhaStages>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
@@ -154,8 +162,8 @@ paged_mha_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   // -------------------------------- consumers --------------------------------
   const int quad = lane >> 2;
   const int qlane = lane & 3;
-  const int r0 = warp * 16 + quad, r1 = r0 + 8;
-  const bool active = warp * 16 < item.n_rows;      // the whole warp, not the lane
+  const int r0 = (kNarrow ? 0 : warp * 16) + quad, r1 = r0 + 8;
+  const bool active = kNarrow || warp * 16 < item.n_rows;      // the whole warp, not the lane
   // ldmatrix lane addressing inside a 64-token sub-tile (before the swizzle)
   const int k_tok_l = ((lane >> 4) << 3) + (lane & 7);        // K: matrices 2,3 -> tokens +8
   const int k_chunk_sel = (lane >> 3) & 1;                    // K: matrices 1,3 -> dims +8
@@ -206,7 +214,75 @@ paged_mha_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       named_bar_sync(1, kMhaConsumerThreads);
     }
-    if (active) {
+    if constexpr (kNarrow) {
+      // ---- this warp's 16 tokens of the tile: S (12 k-steps x 2 n-tiles), softmax, O += P V
+      float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < kMhaKDim / 16; ++ks) {
+        const int chunk = ks * 2 + k_chunk_sel;
+        uint32_t kb[4];
+        ldmatrix_x4(kb, kbase + (chunk >> 3) * kMhaSubBytes + swz128(warp * 16 + k_tok_l, chunk & 7));
+        mma_bf16_16816(sacc[0], qf[ks], kb[0], kb[1]);
+        mma_bf16_16816(sacc[1], qf[ks], kb[2], kb[3]);
+      }
+      const int tok0 = tile * kMhaTile + warp * 16 + qlane * 2;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = tok0 + n * 8 + e;
+          if (j > lim0) sacc[n][e] = -INFINITY;
+          if (j > lim1) sacc[n][2 + e] = -INFINITY;
+          mx0 = fmaxf(mx0, sacc[n][e]);
+          mx1 = fmaxf(mx1, sacc[n][2 + e]);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0 * p.scale_log2;
+      const float ms1 = (mn1 == -INFINITY) ? 0.f : mn1 * p.scale_log2;
+      if (__any_sync(0xffffffffu, (mn0 != m0) || (mn1 != m1))) {
+        const float c0 = fast_exp2(m0 * p.scale_log2 - ms0);
+        const float c1 = fast_exp2(m1 * p.scale_log2 - ms1);
+        l0 *= c0;
+        l1 *= c1;
+#pragma unroll
+        for (int n = 0; n < kMhaVDim / 8; ++n) {
+          o[n][0] *= c0; o[n][1] *= c0; o[n][2] *= c1; o[n][3] *= c1;
+        }
+        m0 = mn0;
+        m1 = mn1;
+      }
+      uint32_t pf[4];
+      {
+        float pr[2][4];
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          pr[n][0] = fast_exp2(fmaf(sacc[n][0], p.scale_log2, -ms0));
+          pr[n][1] = fast_exp2(fmaf(sacc[n][1], p.scale_log2, -ms0));
+          pr[n][2] = fast_exp2(fmaf(sacc[n][2], p.scale_log2, -ms1));
+          pr[n][3] = fast_exp2(fmaf(sacc[n][3], p.scale_log2, -ms1));
+          l0 += pr[n][0] + pr[n][1];
+          l1 += pr[n][2] + pr[n][3];
+        }
+        pf[0] = pack_bf16(pr[0][0], pr[0][1]);
+        pf[1] = pack_bf16(pr[0][2], pr[0][3]);
+        pf[2] = pack_bf16(pr[1][0], pr[1][1]);
+        pf[3] = pack_bf16(pr[1][2], pr[1][3]);
+      }
+#pragma unroll
+      for (int j = 0; j < kMhaVDim / 16; ++j) {
+        const int chunk = j * 2 + v_chunk_sel;
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, vbase + (chunk >> 3) * kMhaSubBytes + swz128(warp * 16 + v_tok_l, chunk & 7));
+        mma_bf16_16816(o[2 * j], pf, vb[0], vb[1]);
+        mma_bf16_16816(o[2 * j + 1], pf, vb[2], vb[3]);
+      }
+    } else if (active) {
       // ---- S = Q K^T: 16 rows x 64 tokens (eight n-tiles of 8)
       float sacc[8][4];
 #pragma unroll
@@ -298,6 +374,80 @@ paged_mha_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if constexpr (kNarrow) {
+    // merge of the four token slices in a fixed order through the (now idle) first stage:
+    // [warp][16 rows][128] sums scaled to the warp's own maximum, then [warp][16] maxima and sums
+    float* mo = reinterpret_cast<float*>(sm.stage[0]);
+    float* mm = mo + kMhaWarps * 16 * kMhaVDim;
+    float* ml = mm + kMhaWarps * 16;
+    named_bar_sync(1, kMhaConsumerThreads);          // every warp has left the tile loop
+#pragma unroll
+    for (int n = 0; n < kMhaVDim / 8; ++n) {
+      *reinterpret_cast<float2*>(mo + (warp * 16 + quad) * kMhaVDim + n * 8 + qlane * 2) = make_float2(o[n][0], o[n][1]);
+      *reinterpret_cast<float2*>(mo + (warp * 16 + quad + 8) * kMhaVDim + n * 8 + qlane * 2) =
+          make_float2(o[n][2], o[n][3]);
+    }
+    if (qlane == 0) {
+      mm[warp * 16 + quad] = m0; mm[warp * 16 + quad + 8] = m1;
+      ml[warp * 16 + quad] = l0; ml[warp * 16 + quad + 8] = l1;
+    }
+    named_bar_sync(1, kMhaConsumerThreads);
+    const int t = threadIdx.x;                       // 128 threads: row t / 8, 16 columns each
+    const int row = t >> 3, col = (t & 7) * 16;
+    if (row >= item.n_rows) return;
+    float g = -INFINITY;
+#pragma unroll
+    for (int w2 = 0; w2 < kMhaWarps; ++w2) g = fmaxf(g, mm[w2 * 16 + row]);
+    float wgt[kMhaWarps], lsum = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < kMhaWarps; ++w2) {
+      const float mw = mm[w2 * 16 + row];
+      wgt[w2] = (mw == -INFINITY) ? 0.f : fast_exp2((mw - g) * p.scale_log2);
+      lsum += ml[w2 * 16 + row] * wgt[w2];
+    }
+    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+    const float lse = lsum > 0.f ? g * p.scale + __logf(lsum) : -INFINITY;
+    float acc[16];
+#pragma unroll
+    for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < kMhaWarps; ++w2) {
+      const float4* src = reinterpret_cast<const float4*>(mo + (w2 * 16 + row) * kMhaVDim + col);
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        const float4 x = src[c4];
+        acc[c4 * 4] += wgt[w2] * x.x; acc[c4 * 4 + 1] += wgt[w2] * x.y;
+        acc[c4 * 4 + 2] += wgt[w2] * x.z; acc[c4 * 4 + 3] += wgt[w2] * x.w;
+      }
+    }
+    const int64_t rix = (int64_t)(item.tok0 + row) * p.num_heads + item.head;
+    if (p.num_splits > 1) {
+      const int64_t prow = (int64_t)item.split * p.num_tokens * p.num_heads + rix;
+      float* dst = p.part_o + prow * kMhaVDim + col;
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4)
+        *reinterpret_cast<float4*>(dst + c4 * 4) = make_float4(acc[c4 * 4] * inv, acc[c4 * 4 + 1] * inv,
+                                                               acc[c4 * 4 + 2] * inv, acc[c4 * 4 + 3] * inv);
+      if ((t & 7) == 0) p.part_lse[prow] = lse;
+    } else {
+      const int64_t off = rix * kMhaVDim + col;
+      if (p.out_is_f32) {
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4)
+          *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + off + c4 * 4) =
+              make_float4(acc[c4 * 4] * inv, acc[c4 * 4 + 1] * inv, acc[c4 * 4 + 2] * inv, acc[c4 * 4 + 3] * inv);
+      } else {
+        uint32_t pk[8];
+#pragma unroll
+        for (int c2 = 0; c2 < 8; ++c2) pk[c2] = pack_bf16(acc[c2 * 2] * inv, acc[c2 * 2 + 1] * inv);
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off);
+        dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      }
+      if (p.lse_out && (t & 7) == 0) p.lse_out[rix] = lse;
+    }
+    return;
+  }
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     const int row = half ? r1 : r0;
@@ -379,10 +529,13 @@ extern "C" int b200_mha_plan(const int32_t* cu_q, const int32_t* kv_lens, const 
   }
   const int num_tokens = prev;
   const int64_t base_items = (int64_t)blocks.size() * num_heads;
+  bool narrow = true;
+  for (const Block& blk : blocks) narrow &= blk.n_rows <= 16;
   int splits = 1;
   if (base_items > 0) {
-    // two CTAs per SM, and twice that many items to even out their lengths
-    const int64_t want = 4LL * num_ctas;
+    // wide: two CTAs per SM, and twice that many items to even out their lengths; narrow: one
+    // CTA per SM, three items each
+    const int64_t want = (narrow ? 3LL : 4LL) * num_ctas;
     splits = (int)std::min<int64_t>(kMhaMaxSplits, (want + base_items - 1) / base_items);
     splits = std::max(1, std::min(splits, max_tiles / 4));             // at least four tiles per split
   }
@@ -409,6 +562,7 @@ extern "C" int b200_mha_plan(const int32_t* cu_q, const int32_t* kv_lens, const 
   plan_host[1] = (int32_t)items.size();
   plan_host[2] = splits;
   plan_host[3] = num_tokens;
+  plan_host[4] = narrow ? 1 : 0;
   if (!items.empty())
     std::copy(reinterpret_cast<const int32_t*>(items.data()),
               reinterpret_cast<const int32_t*>(items.data()) + items.size() * kMhaItemInts,
@@ -416,6 +570,7 @@ extern "C" int b200_mha_plan(const int32_t* cu_q, const int32_t* kv_lens, const 
   info->num_items = (int32_t)items.size();
   info->num_splits = splits;
   info->num_tokens = num_tokens;
+  info->narrow = narrow ? 1 : 0;
   info->plan_ints = (int32_t)(kMhaHeaderInts + items.size() * kMhaItemInts);
   info->total_tiles = total_tiles * num_heads;
   return B200_OK;
@@ -494,17 +649,19 @@ extern "C" int b200_paged_mha(const void* q, int64_t q_stride, const void* key_c
   p.scale_log2 = scale * 1.4426950408889634f;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t smem = sizeof(MhaSmem) + 1024;
-  static bool attr_set[64] = {false};
+  const int which = info->narrow ? 1 : 0;
+  auto kernel = which ? paged_mha_kernel<true> : paged_mha_kernel<false>;
+  const size_t smem = (which ? sizeof(MhaSmem<kMhaNarrowStages>) : sizeof(MhaSmem<kMhaWideStages>)) + 1024;
+  static bool attr_set[2][64] = {{false}, {false}};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 64 || !attr_set[dev]) {
-    rc = check_cuda(cudaFuncSetAttribute(paged_mha_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+  if (dev >= 64 || !attr_set[which][dev]) {
+    rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                     "paged_mha smem attribute");
     if (rc) return rc;
-    if (dev < 64) attr_set[dev] = true;
+    if (dev < 64) attr_set[which][dev] = true;
   }
-  rc = check_cuda(launch_pdl(paged_mha_kernel, dim3(info->num_items), dim3(kMhaThreads), smem, s, k_map, v_map, p),
+  rc = check_cuda(launch_pdl(kernel, dim3(info->num_items), dim3(kMhaThreads), smem, s, k_map, v_map, p),
                   "paged_mha launch");
   if (rc || splits == 1) return rc;
   return b200_lse_combine(part_o, part_lse, rows * kMhaVDim, rows, splits, rows, kMhaVDim, out, out_is_f32,

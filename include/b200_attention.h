@@ -381,6 +381,8 @@ typedef struct b200_mha_plan_info {
   int32_t num_splits;    /* key splits per (block of rows, head), 1..8           */
   int32_t num_tokens;    /* packed query tokens the plan covers                  */
   int32_t plan_ints;     /* int32 words of the plan to copy to the device        */
+  int32_t narrow;        /* 1: every block has <= 16 rows (decode / verify step)  */
+  int32_t reserved;
   int64_t total_tiles;   /* 64-token tiles streamed by all items                 */
 } b200_mha_plan_info;
 

@@ -189,6 +189,10 @@ def test_mha_plan_covers_every_row_and_key_once(lib):
                     at = t1
                 assert at == n_tiles
         assert info.total_tiles == sum(lengths)
+    # a step with a block of more than 16 rows is not "narrow"; decode / verify steps are
+    assert _mha_plan(lib, cu, kv, heads, 148)[0].narrow == 0
+    assert _mha_plan(lib, [1, 3, 19], [500, 70, 9000], heads, 148)[0].narrow == 1
+    assert _mha_plan(lib, [1, 18], [500, 70], heads, 148)[0].narrow == 0
     # one CTA wanted: no splits; many: the longest block is cut
     assert _mha_plan(lib, cu, kv, heads, 1)[0].num_splits == 1
     assert _mha_plan(lib, cu, kv, heads, 4000)[0].num_splits == 8
