@@ -206,6 +206,31 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
     p.trace[blockIdx.x * 16 + 15] = clock64();
   }
 #endif
+  // While the kernel in front drains: the first tiles of this CTA's first item are asked into
+  // L2.  Hints only - the block ids are read past the L1 (nothing stale can stick there) and used
+  // for nothing but the prefetch addresses; the loads proper follow the dependency wait and then
+  // find a warm L2 instead of paying the cold trip to HBM (the table and the cache rows are
+  // normally written long before; if the kernel in front does write them, the hint is merely
+  // wasted).
+  if (warp == kConsumerWarps && item_begin < item_end) {
+    constexpr int kHintTiles = 4;
+    const int nbox = p.boxes_per_tile;
+    const int n_hint = min(r1.w - r1.z, kHintTiles) * nbox;          // tile_end - tile_begin of the first item
+    if (lane < n_hint && r2.x > 0) {
+      const int tile = r1.z + lane / nbox, box = lane % nbox;
+      int lb = ((tile * kTileTokens) >> p.block_shift) + box;
+      const int last_block = (r2.x - 1) >> p.block_shift;
+      lb = lb > last_block ? last_block : lb;
+      const int bid = __ldcg(p.block_table + (int64_t)r1.x * p.bt_stride + lb);
+      if (bid >= 0 && bid < p.num_blocks) {
+        const int tok = (tile * kTileTokens + box * p.box_tokens) & (p.block_size - 1);
+        tma_prefetch_4d(&k_map, 0, r1.y, tok, bid);
+        tma_prefetch_4d(&k_map, 64, r1.y, tok, bid);
+        tma_prefetch_4d(&v_map, 0, r1.y, tok, bid);
+        tma_prefetch_4d(&v_map, 64, r1.y, tok, bid);
+      }
+    }
+  }
   grid_dep_launch();              // the next kernel may be scheduled; it waits for this grid itself
   grid_dep_wait();                // q, the block table and the step's new cache rows come from earlier kernels
 #ifdef B200_TRACE
