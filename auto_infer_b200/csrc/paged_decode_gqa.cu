@@ -362,6 +362,19 @@ paged_decode_gqa_kernel(const __grid_constant__ CUtensorMap k_map,
   // loads fly while the warps merge and write the current item.
   uint32_t qf[8][4];
   auto load_q = [&](const DecodeItem& qi) {
+    if constexpr (kWrite) {
+      // the item's new K / V rows (if its tiles hold them) are asked into L1 now, so that the
+      // patch of the tile they fall in does not wait for a trip to L2
+      if (qi.tile_end * kTileTokens >= qi.kv_len && warp < 4) {
+        const int row = warp;                                  // one row per warp, the first four
+        if (row < qi.q_len) {
+          const int64_t tok = qi.q_start + row;
+          const __nv_bfloat16* src = (lane >= 16 ? wp.v_new + tok * wp.v_new_stride : wp.k_new + tok * wp.k_new_stride) +
+                                     qi.kv_head * kHeadDim + (lane & 15) * 8;
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(src));
+        }
+      }
+    }
     const int qrows = qi.q_len * G;
     const int r0 = quad, r1 = quad + 8;
     const __nv_bfloat16* q0 = nullptr;
