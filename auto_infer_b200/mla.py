@@ -34,22 +34,23 @@ class B200MlaBackend(AttentionBackend):
     """Constructor keywords follow ``MlaFIABackend`` (mla.py:190-211).  Only the
     absorbed form is built (``absorb`` must stay True): it is the one whose cache
     is 9x smaller and whose attention is a single dense contraction.  ``num_heads`` is
-    the number of heads THIS rank holds and may not exceed 16 (one 16-row MMA tile per
-    sequence): DeepSeek-V3's 128 heads run at a head-parallel degree of 8 or more."""
+    the number of heads THIS rank holds.  The kernel takes up to 16 heads at a time (one
+    16-row MMA tile per sequence): a rank with more heads runs it once per slice of
+    ``heads_per_launch`` heads, each slice streaming the latent cache again, so DeepSeek-V3's
+    128 heads want a head-parallel degree of 8 (MLA has no all-reduce inside attention,
+    auto_infer/layers/attention/mla.py:282-285) and merely work without it."""
 
-    MAX_HEADS_PER_RANK = 16
+    MAX_HEADS_PER_LAUNCH = 16
 
     def __init__(self, w: dict, *, num_heads: int, qk_nope: int, qk_rope: int, v_head_dim: int,
                  kv_lora_rank: int, q_lora_rank, rms_eps: float, softmax_scale: float,
                  num_layers: int, device, dtype, absorb: bool = True, layer_prefix=None):
         if not absorb:
             raise NotImplementedError("the B200 MLA backend implements the absorbed latent form only")
-        if num_heads > self.MAX_HEADS_PER_RANK:
-            raise ValueError(
-                f"the latent decode kernel takes q_len * heads <= {self.MAX_HEADS_PER_RANK} rows per "
-                f"sequence; {num_heads} heads per rank need tensor parallelism of at least "
-                f"{(num_heads + self.MAX_HEADS_PER_RANK - 1) // self.MAX_HEADS_PER_RANK} "
-                "(MLA has no all-reduce inside attention, auto_infer/layers/attention/mla.py:282-285)")
+        if num_heads <= 0:
+            raise ValueError("num_heads must be positive")
+        # equal slices: the largest divisor of num_heads that fits one launch
+        self.heads_per_launch = max(h for h in range(1, self.MAX_HEADS_PER_LAUNCH + 1) if num_heads % h == 0)
         self.w = w
         self.num_heads = num_heads
         self.qk_nope = qk_nope
@@ -127,8 +128,23 @@ class B200MlaBackend(AttentionBackend):
     def _latent_attn(self, layer_idx: int, q_latent: torch.Tensor, ctx) -> torch.Tensor:
         latent_cache = ctx.kv_caches[layer_idx][0]
         plan, block_table = self._plan(ctx, q_latent.device)
-        return ops.mla_decode_absorbed(q_latent, latent_cache, block_table, plan,
-                                       self.softmax_scale, kv_lora_rank=self.kv_lora_rank)
+        return self._run_slices(q_latent, latent_cache, block_table, plan)
+
+    def _run_slices(self, q_latent: torch.Tensor, latent_cache: torch.Tensor, block_table: torch.Tensor,
+                    plan) -> torch.Tensor:
+        """The kernel once per slice of ``heads_per_launch`` heads (one launch when the rank holds
+        at most 16): a slice is a strided view of q_latent, its rows go to their columns of out."""
+        h = self.heads_per_launch
+        if h == self.num_heads:
+            return ops.mla_decode_absorbed(q_latent, latent_cache, block_table, plan,
+                                           self.softmax_scale, kv_lora_rank=self.kv_lora_rank)
+        out = torch.empty(q_latent.shape[0], self.num_heads, self.kv_lora_rank, dtype=q_latent.dtype,
+                          device=q_latent.device)
+        for first in range(0, self.num_heads, h):
+            part = ops.mla_decode_absorbed(q_latent[:, first:first + h], latent_cache, block_table, plan,
+                                           self.softmax_scale, kv_lora_rank=self.kv_lora_rank)
+            out[:, first:first + h].copy_(part)
+        return out
 
     def _plan(self, ctx, device):
         """One plan per step.  The kernel takes q_len * heads <= 16 rows per
@@ -136,11 +152,11 @@ class B200MlaBackend(AttentionBackend):
         single-token sequences that share the block-table row and end at
         kv_len - q_len + 1 + i keys, which is the same bottom-right causal mask."""
         cached = getattr(ctx, "_b200_mla_plan", None)
-        if cached is not None and cached[0] == (self.num_heads, str(device)):
+        if cached is not None and cached[0] == (self.heads_per_launch, str(device)):
             return cached[1], cached[2]
         cu, kv = list(ctx.cu_seqlens_q), list(ctx.seqlens_kv)
         block_table = ctx.block_table
-        max_q = max(1, 16 // self.num_heads)
+        max_q = max(1, 16 // self.heads_per_launch)
         prev, wide = 0, False
         for end in cu:
             wide |= (end - prev) > max_q
@@ -161,11 +177,11 @@ class B200MlaBackend(AttentionBackend):
                 0, torch.tensor(rows, dtype=torch.long, device=block_table.device))
         plan = self._make_plan(cu, kv, device, wide)
         assert plan.skipped_seqs == 0
-        setattr(ctx, "_b200_mla_plan", ((self.num_heads, str(device)), plan, block_table))
+        setattr(ctx, "_b200_mla_plan", ((self.heads_per_launch, str(device)), plan, block_table))
         return plan, block_table
 
     def _make_plan(self, cu, kv, device, wide: bool):
-        return ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank)
+        return ops.MlaDecodePlan(cu, kv, self.heads_per_launch, device, kv_lora_rank=self.kv_lora_rank)
 
 
 @dataclass(frozen=True)
@@ -212,7 +228,7 @@ class B200GraphMlaBackend(B200MlaBackend):
 
     def _make_plan(self, cu, kv, device, wide: bool):
         if wide:        # per-row expansion: not replayable, and never recorded
-            return ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank)
+            return ops.MlaDecodePlan(cu, kv, self.heads_per_launch, device, kv_lora_rank=self.kv_lora_rank)
         key = (len(cu), str(device))
         plan = self._plan_pool.get(key)
         if plan is None:
@@ -220,7 +236,7 @@ class B200GraphMlaBackend(B200MlaBackend):
                 raise RuntimeError(
                     "capture needs one eager step with the same context first (capturing False): the "
                     "plan's buffers cannot be allocated while the stream is being captured")
-            plan = ops.MlaDecodePlan(cu, kv, self.num_heads, device, kv_lora_rank=self.kv_lora_rank,
+            plan = ops.MlaDecodePlan(cu, kv, self.heads_per_launch, device, kv_lora_rank=self.kv_lora_rank,
                                      capacity_seqs=len(cu))
             self._plan_pool[key] = plan
         else:
@@ -231,7 +247,7 @@ class B200GraphMlaBackend(B200MlaBackend):
         if not self.capturing:
             return super()._latent_attn(layer_idx, q_latent, ctx)
         cached = getattr(ctx, "_b200_mla_plan", None)
-        if cached is None or cached[0] != (self.num_heads, str(q_latent.device)) or not cached[1].replayable:
+        if cached is None or cached[0] != (self.heads_per_launch, str(q_latent.device)) or not cached[1].replayable:
             raise RuntimeError(
                 "capture needs one eager step with the same context first (capturing False), and a "
                 "decode-shaped step: a prefill chunk cannot be recorded")
@@ -240,15 +256,14 @@ class B200GraphMlaBackend(B200MlaBackend):
             if pooled is plan:                      # the plan now belongs to this capture
                 del self._plan_pool[key]
         latent_cache = ctx.kv_caches[layer_idx][0]
-        out = ops.mla_decode_absorbed(q_latent, latent_cache, block_table, plan, self.softmax_scale,
-                                      kv_lora_rank=self.kv_lora_rank)
+        out = self._run_slices(q_latent, latent_cache, block_table, plan)
         self.reg.append(_GraphMlaRegistration(plan, layer_idx, q_latent, out))
         return out
 
     # -- per-step update (graph_fia.py:87-104) --------------------------------
     def _refill(self, plan, ctx, stream) -> None:
         cu, kv = list(ctx.cu_seqlens_q), list(ctx.seqlens_kv)
-        max_q = max(1, 16 // self.num_heads)
+        max_q = max(1, 16 // self.heads_per_launch)
         prev = 0
         for end in cu:
             if end - prev > max_q:

@@ -137,3 +137,26 @@ def test_backend_block_decode_and_prefill_rows():
     torch.testing.assert_close(caches[0][0].cpu().float(), ref_cache.float(), atol=4e-2, rtol=2e-2)
     torch.testing.assert_close(out.cpu().float(), ref.float(), atol=3e-2, rtol=3e-2)
     assert ops.read_status("cuda") == 0
+
+
+def test_more_heads_than_one_launch_holds_run_as_slices():
+    """40 heads on one rank: four launches of 10 heads each over the same latent cache and plan (the
+    two-token sequence exceeds 16 rows per launch and takes the per-row expansion)."""
+    from auto_infer_b200 import ops, synth
+    from auto_infer_b200.forward_context import ForwardContext
+    from auto_infer_b200.mla import B200MlaBackend
+    heads = 40
+    b = synth.build_mla_batch("sliced heads", [(1, 70), (1, 600), (2, 129), (1, 1)], heads, 12, 91)
+    d = b.to("cuda")
+    backend = B200MlaBackend({}, num_heads=heads, qk_nope=128, qk_rope=64, v_head_dim=128, kv_lora_rank=512,
+                             q_lora_rank=None, rms_eps=1e-6, softmax_scale=b.scale, num_layers=1, device="cuda",
+                             dtype=torch.bfloat16)
+    assert backend.heads_per_launch == 10
+    ctx = ForwardContext(None, None, d.slot_mapping, d.block_table, b.cu_seqlens_q, b.seqlens_kv, None, backend,
+                         [(d.kv_cache, d.kv_cache)], True)
+    out = backend.latent_attention(0, d.q, d.k_new, ctx).cpu()
+    orc.write_kv(b.k_new, None, b.kv_cache, None, b.slot_mapping.tolist())
+    assert torch.equal(d.kv_cache.cpu(), b.kv_cache)
+    ref = orc.paged_attention(b.q, b.kv_cache, b.kv_cache, b.block_table, b.cu_seqlens_q, b.seqlens_kv, b.scale)
+    assert_attention_close(out, ref[..., :512], what="40 heads in slices of 10")
+    assert ops.read_status("cuda") == 0

@@ -240,13 +240,14 @@ def test_install_into_auto_infer_serves_the_reference_builders():
         ref.build_mtp_attention_backend(_gqa_model("gqa_b200"), "dense", "model.mtp_layers.0.")
 
 
-def test_mla_backend_refuses_more_heads_than_the_kernel_holds():
-    """128 heads on one rank (DeepSeek-V3 without head parallelism) must fail at construction
-    with the reason, not on the first step."""
-    with pytest.raises(ValueError, match="tensor parallelism of at least 8"):
-        B200MlaBackend({}, num_heads=128, qk_nope=128, qk_rope=64, v_head_dim=128, kv_lora_rank=512,
-                       q_lora_rank=None, rms_eps=1e-6, softmax_scale=192 ** -0.5, num_layers=1,
-                       device="cpu", dtype=torch.bfloat16)
-    B200MlaBackend({}, num_heads=16, qk_nope=128, qk_rope=64, v_head_dim=128, kv_lora_rank=512,
-                   q_lora_rank=None, rms_eps=1e-6, softmax_scale=192 ** -0.5, num_layers=1,
-                   device="cpu", dtype=torch.bfloat16)
+def test_mla_backend_slices_heads_beyond_one_launch():
+    """More than 16 heads on one rank (DeepSeek-V3's 128 without head parallelism) run as equal
+    slices of at most 16 heads per launch; the slice is the largest divisor that fits."""
+    def heads(n):
+        return B200MlaBackend({}, num_heads=n, qk_nope=128, qk_rope=64, v_head_dim=128, kv_lora_rank=512,
+                              q_lora_rank=None, rms_eps=1e-6, softmax_scale=192 ** -0.5, num_layers=1,
+                              device="cpu", dtype=torch.bfloat16).heads_per_launch
+    assert heads(16) == 16 and heads(128) == 16 and heads(8) == 8
+    assert heads(24) == 12 and heads(20) == 10 and heads(17) == 1
+    with pytest.raises(ValueError):
+        heads(0)
