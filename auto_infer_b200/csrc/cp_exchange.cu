@@ -118,16 +118,28 @@ cp_exchange_combine_kernel(const ExchangeParams p) {
     const int lane = threadIdx.x & 31;
     const int warps = kExThreads >> 5;
     for (int64_t row = row0 + (threadIdx.x >> 5); row < row1; row += warps) {
+      // The lines of the R sources are independent: four loads are issued together and only a
+      // line that has not arrived yet is polled, so a row costs about R / 4 trips to memory
+      // instead of R.
       bool ok = true;
       float mx = -INFINITY;
-      for (int r = 0; r < p.world && ok; ++r) {
-        uint4 v;
-        ok = wait_line(base + r * src_lines + row * lpr + (lpr - 1), seq, p.wait_limit_ns, v);
-        mx = fmaxf(mx, __uint_as_float(v.x));
+      const uint4* lse_line = base + row * lpr + (lpr - 1);
+      for (int r0 = 0; r0 < p.world && ok; r0 += 4) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (r0 + u < p.world) v[u] = ld_line(lse_line + (int64_t)(r0 + u) * src_lines);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (r0 + u >= p.world || !ok) continue;
+          if (v[u].y != seq || v[u].w != seq)
+            ok = wait_line(lse_line + (int64_t)(r0 + u) * src_lines, seq, p.wait_limit_ns, v[u]);
+          mx = fmaxf(mx, __uint_as_float(v[u].x));
+        }
       }
       float wsum = 0.f;
       for (int r = 0; r < p.world && ok; ++r) {
-        const float l = __uint_as_float(ld_line(base + r * src_lines + row * lpr + (lpr - 1)).x);
+        const float l = __uint_as_float(ld_line(lse_line + (int64_t)r * src_lines).x);
         wsum += (l == -INFINITY) ? 0.f : __expf(l - mx);
       }
       const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
@@ -137,13 +149,25 @@ cp_exchange_combine_kernel(const ExchangeParams p) {
         acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
         const int line = lane + 32 * k;
         if (line >= lpr - 1) continue;
-        for (int r = 0; r < p.world && ok; ++r) {
-          const float l = __uint_as_float(ld_line(base + r * src_lines + row * lpr + (lpr - 1)).x);
-          const float w = (l == -INFINITY) ? 0.f : __expf(l - mx) * inv;
-          uint4 v;
-          ok = wait_line(base + r * src_lines + row * lpr + line, seq, p.wait_limit_ns, v);
-          const float2 a = unpack_bf16(v.x), b = unpack_bf16(v.z);
-          acc[k].x += w * a.x; acc[k].y += w * a.y; acc[k].z += w * b.x; acc[k].w += w * b.y;
+        const uint4* pay = base + row * lpr + line;
+        for (int r0 = 0; r0 < p.world && ok; r0 += 4) {
+          uint4 v[4], lv[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (r0 + u < p.world) {
+              v[u] = ld_line(pay + (int64_t)(r0 + u) * src_lines);
+              lv[u] = ld_line(lse_line + (int64_t)(r0 + u) * src_lines);
+            }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (r0 + u >= p.world || !ok) continue;
+            if (v[u].y != seq || v[u].w != seq)
+              ok = wait_line(pay + (int64_t)(r0 + u) * src_lines, seq, p.wait_limit_ns, v[u]);
+            const float l = __uint_as_float(lv[u].x);
+            const float w = (l == -INFINITY) ? 0.f : __expf(l - mx) * inv;
+            const float2 a = unpack_bf16(v[u].x), b = unpack_bf16(v[u].z);
+            acc[k].x += w * a.x; acc[k].y += w * a.y; acc[k].z += w * b.x; acc[k].w += w * b.y;
+          }
         }
       }
       if (!__all_sync(0xffffffffu, ok)) {              // a peer is gone: this and the remaining rows stay as they are
