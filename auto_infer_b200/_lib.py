@@ -73,6 +73,10 @@ SIGNATURES = {
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, POINTER(PrefillPlanInfo), c_int, c_int, c_int, c_float,
         c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
+    "b200_paged_prefill_gqa_on": (c_int, [
+        c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+        c_void_p, POINTER(PrefillPlanInfo), c_int, c_int, c_int, c_int, c_float,
+        c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200_paged_prefill_gqa_replayable": (c_int, [
         c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
         c_void_p, c_int, c_int, c_int, c_int, c_float,

@@ -765,9 +765,9 @@ static int launch_prefill(const char* who, const void* q, int64_t q_stride, cons
                           const int32_t* block_table, int64_t bt_stride, int32_t* plan_dev,
                           const b200_prefill_plan_info* info, int num_tokens, int num_q_heads,
                           int num_kv_heads, int head_dim, float scale, void* out, int out_is_f32,
-                          float* lse_out, int32_t* status, void* stream) {
+                          float* lse_out, int32_t* status, void* stream, int max_ctas = 0) {
   if (!q || !key_cache || !value_cache || !block_table || !plan_dev || !out || num_blocks <= 0 ||
-      num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_tokens < 0) {
+      num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads || num_tokens < 0 || max_ctas < 0) {
     set_last_error("%s: null pointer or bad head counts", who);
     return B200_EINVAL;
   }
@@ -839,6 +839,7 @@ static int launch_prefill(const char* who, const void* q, int64_t q_stride, cons
   int grid = b200_sm_count();
   if (grid <= 0) grid = 148;
   if (info && grid > info->num_items) grid = info->num_items;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;     // the rest of the SMs are left to another kernel
   return check_cuda(launch_pdl(paged_prefill_tc_kernel, dim3(grid), dim3(kTcThreads), smem_tc,
                                static_cast<cudaStream_t>(stream), k_map, v_map, q_map, p),
                     "paged_prefill_gqa launch");
@@ -871,4 +872,21 @@ extern "C" int b200_paged_prefill_gqa_replayable(const void* q, int64_t q_stride
   return launch_prefill("paged_prefill_gqa_replayable", q, q_stride, key_cache, value_cache, num_blocks,
                         block_size, block_table, bt_stride, plan_dev, nullptr, num_tokens, num_q_heads,
                         num_kv_heads, head_dim, scale, out, out_is_f32, lse_out, status, stream);
+}
+
+extern "C" int b200_paged_prefill_gqa_on(const void* q, int64_t q_stride, const void* key_cache,
+                                         const void* value_cache, int num_blocks, int block_size,
+                                         const int32_t* block_table, int64_t bt_stride,
+                                         int32_t* plan_dev, const b200_prefill_plan_info* info, int max_ctas,
+                                         int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                                         void* out, int out_is_f32, float* lse_out, int32_t* status,
+                                         void* stream) {
+  if (!info) {
+    set_last_error("paged_prefill_gqa_on: plan info is null");
+    return B200_EINVAL;
+  }
+  if (info->num_items == 0) return B200_OK;
+  return launch_prefill("paged_prefill_gqa_on", q, q_stride, key_cache, value_cache, num_blocks, block_size,
+                        block_table, bt_stride, plan_dev, info, info->num_tokens, num_q_heads, num_kv_heads,
+                        head_dim, scale, out, out_is_f32, lse_out, status, stream, max_ctas);
 }

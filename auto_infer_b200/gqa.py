@@ -27,6 +27,7 @@ class B200GqaBackend(AttentionBackend):
     same keyword set."""
 
     _one_launch_step = True           # paged_attention may fold the slot write into the attention launch
+    _overlap_mixed = True             # a mixed step may run its two kernels side by side on disjoint SMs
 
     def __init__(self, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                  num_layers: int, device, dtype, w: dict = None, layer_prefix=None, rms_eps=None,
@@ -45,6 +46,7 @@ class B200GqaBackend(AttentionBackend):
         self.rms_eps = rms_eps
         self.tp_group = tp_group
         self._meta_pool: dict = {}        # refillable per-step plans, one per head geometry
+        self._side_stream = None          # second stream of a mixed step run side by side
 
     # -- cache ------------------------------------------------------------
     def alloc_kv_caches(self, num_blocks: int, block_size: int) -> list:
@@ -91,8 +93,25 @@ class B200GqaBackend(AttentionBackend):
               ctx) -> torch.Tensor:
         cache = ctx.kv_caches[layer_idx]
         meta = step_metadata(ctx, self.n_q_heads, self.n_kv_heads, self.head_dim, q.device,
-                             pool=self._meta_pool)
+                             pool=self._meta_pool, split_mixed=self._overlap_mixed)
         out = torch.empty(q.shape[0], self.n_q_heads, self.head_dim, dtype=q.dtype, device=q.device)
+        if meta.prefill is not None and meta.prefill_ctas and meta.decode.info.num_items:
+            # A mixed step, side by side: the wide-query kernel (tensor pipe, shared memory) on
+            # its share of the SMs from a second stream, the decode kernel (memory bandwidth) on
+            # the rest from this one; they write disjoint rows of `out` and join before returning.
+            cur = torch.cuda.current_stream(q.device)
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(q.device)
+            fork, join = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(cur)
+            self._side_stream.wait_event(fork)
+            with torch.cuda.stream(self._side_stream):
+                ops.paged_prefill_gqa(q, cache[0], cache[1], ctx.block_table, meta.prefill, self.scale,
+                                      out=out, max_ctas=meta.prefill_ctas)
+                join.record(self._side_stream)
+            ops.paged_decode_gqa(q, cache[0], cache[1], ctx.block_table, meta.decode, self.scale, out=out)
+            cur.wait_event(join)
+            return out
         if meta.decode.info.num_items:
             ops.paged_decode_gqa(q, cache[0], cache[1], ctx.block_table, meta.decode, self.scale,
                                  out=out)
@@ -109,7 +128,7 @@ class B200GqaBackend(AttentionBackend):
         stores the new rows itself."""
         cache = ctx.kv_caches[layer_idx]
         meta = step_metadata(ctx, self.n_q_heads, self.n_kv_heads, self.head_dim, q.device,
-                             pool=self._meta_pool)
+                             pool=self._meta_pool, split_mixed=self._overlap_mixed)
         if meta.prefill is None and meta.decode.info.num_items and self._one_launch_step:
             return ops.paged_decode_gqa_write(q, k, v, ctx.slot_mapping, cache[0], cache[1], ctx.block_table,
                                               meta.decode, self.scale)
@@ -151,6 +170,7 @@ class B200GraphGqaBackend(B200GqaBackend):
     supports_prefill_graph = True       # the wide-query launch is replayable too (gears of a fixed token count)
 
     _one_launch_step = False          # the recorded launches go through _write_kv / _attn
+    _overlap_mixed = False            # a recorded gear keeps its launches on one stream
 
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)

@@ -438,10 +438,12 @@ class PrefillPlan:
 def paged_prefill_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
                       block_table: torch.Tensor, plan: PrefillPlan, scale: float,
                       out: Optional[torch.Tensor] = None, out_f32: bool = False,
-                      lse_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      lse_out: Optional[torch.Tensor] = None, max_ctas: int = 0) -> torch.Tensor:
     """Paged GQA attention for wide query blocks (chunked prefill, multi-token
     verify); replaces ``paged_fia`` (auto_infer/layers/attention/base.py:48-61)
-    for the sequences in ``plan``.  Other rows of ``out`` are left untouched."""
+    for the sequences in ``plan``.  Other rows of ``out`` are left untouched.
+    ``max_ctas`` > 0 keeps the launch to that many SMs (a mixed step runs the decode
+    kernel on the others at the same time)."""
     _need_cuda(q, key_cache, value_cache, block_table)
     lib = _lib.load()
     t, n_q, d = q.shape
@@ -466,6 +468,14 @@ def paged_prefill_gqa(q: torch.Tensor, key_cache: torch.Tensor, value_cache: tor
                 q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
                 num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
                 plan.dev.data_ptr(), t, n_q, n_kv, d, float(scale),
+                out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
+                lse_out.data_ptr() if lse_out is not None else None,
+                status_word(q.device).data_ptr(), _stream_ptr(q.device))
+        elif max_ctas > 0:
+            rc = lib.b200_paged_prefill_gqa_on(
+                q.data_ptr(), q.stride(0), key_cache.data_ptr(), value_cache.data_ptr(),
+                num_blocks, block_size, block_table.data_ptr(), block_table.stride(0),
+                plan.dev.data_ptr(), ctypes.byref(plan.info), int(max_ctas), n_q, n_kv, d, float(scale),
                 out.data_ptr(), 1 if out.dtype == torch.float32 else 0,
                 lse_out.data_ptr() if lse_out is not None else None,
                 status_word(q.device).data_ptr(), _stream_ptr(q.device))

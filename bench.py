@@ -290,13 +290,42 @@ def side_config(name, device):
             return lambda: ops.paged_prefill_gqa(b.q, caches[i][0], caches[i][1], b.block_table, meta.prefill,
                                                  b.scale, out=out)
 
-        us, best = layer_rotation_time(make_full, layers, device)
+        us_seq, _ = layer_rotation_time(make_full, layers, device)
         us_dec, _ = layer_rotation_time(make_dec, layers, device)
         us_pre, _ = layer_rotation_time(make_pre, layers, device)
+        # the step as the backend runs it: the two kernels side by side on disjoint SMs (the decode
+        # plan built for its share), when the cost model expects a gain
+        from auto_infer_b200.metadata import mixed_split, scan_step
+        _, dec_b, pre_t = scan_step(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim)
+        n_pre = mixed_split(dec_b, pre_t, ops.sm_count(device))
+        us, best = us_seq, us_seq
+        if n_pre:
+            split = StepMetadata(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, device,
+                                 prefill_ctas=n_pre)
+            side = torch.cuda.Stream(device)
+
+            def make_side_by_side(i):
+                def step():
+                    ops.reshape_and_cache(b.k_new, b.v_new, caches[i][0], caches[i][1], b.slot_mapping)
+                    cur = torch.cuda.current_stream(device)
+                    fork, join = torch.cuda.Event(), torch.cuda.Event()
+                    fork.record(cur)
+                    side.wait_event(fork)
+                    with torch.cuda.stream(side):
+                        ops.paged_prefill_gqa(b.q, caches[i][0], caches[i][1], b.block_table, split.prefill,
+                                              b.scale, out=out, max_ctas=n_pre)
+                        join.record(side)
+                    ops.paged_decode_gqa(b.q, caches[i][0], caches[i][1], b.block_table, split.decode, b.scale,
+                                         out=out)
+                    cur.wait_event(join)
+                return step
+
+            us, best = layer_rotation_time(make_side_by_side, layers, device)
         # causal-aware flops of the four 512-token chunks over prefixes 0/1024/2048/4096
         flops = sum(4 * 32 * 128 * (512 * p + 131328) for p in (0, 1024, 2048, 4096))
         dec_bytes = sum(b.seqlens_kv[:60]) * 4096 + 2 * 60 * 32 * 128 * 2
         return {"us_per_layer_step": round(us, 2), "best_us": round(best, 2),
+                "one_after_the_other_us": round(us_seq, 2), "prefill_sms_side_by_side": n_pre,
                 "decode_rows_us": round(us_dec, 2), "decode_rows_gbs": round(dec_bytes / us_dec / 1e3, 1),
                 "decode_rows_hbm_frac": round(dec_bytes / us_dec / 1e3 / hbm_peak, 3),
                 "prefill_chunks_us": round(us_pre, 2), "prefill_gflop": round(flops / 1e9, 2),

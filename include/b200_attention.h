@@ -254,6 +254,21 @@ int b200_paged_prefill_gqa(const void* q, int64_t q_stride,
                            void* out, int out_is_f32, float* lse_out,
                            int32_t* status, void* stream);
 
+/* The same on at most max_ctas SMs (0 = all), for a mixed step whose decode rows
+ * and prefill chunks run side by side: the decode kernel is bound by memory
+ * bandwidth and the wide-query kernel by the tensor pipe and shared memory, so a
+ * step that gives each its share of the SMs (decode plan built for the other
+ * num_ctas, the two launches on two streams) finishes sooner than one that runs
+ * them one after the other on all SMs.  The kernels do not wait on one another. */
+int b200_paged_prefill_gqa_on(const void* q, int64_t q_stride,
+                              const void* key_cache, const void* value_cache,
+                              int num_blocks, int block_size,
+                              const int32_t* block_table, int64_t bt_stride,
+                              int32_t* plan_dev, const b200_prefill_plan_info* info, int max_ctas,
+                              int num_q_heads, int num_kv_heads, int head_dim, float scale,
+                              void* out, int out_is_f32, float* lse_out,
+                              int32_t* status, void* stream);
+
 /* The wide-query attention as a launch that can be recorded once and replayed
  * for other steps (the prefill gears of the reference's graph runner,
  * auto_infer/worker/graph_decode_runner.py:360-414): the grid is the SM count,

@@ -175,3 +175,24 @@ def test_config2_full_size_mixed_batch():
                               b.seqlens_kv, b.scale, literal_max_kv=0)
     assert_attention_close(out, ref, what="config 2 (60 decode rows + 4 chunks)")
     assert ops.read_status("cuda") == 0
+    # this step is one the backend runs side by side (wide-query kernel on its share of the SMs,
+    # decode kernel on the rest); one after the other on all SMs gives the same rows, up to the
+    # order in which a cut pair's pieces are summed (the decode plan is another one)
+    from auto_infer_b200.metadata import cached_step_metadata
+    meta = cached_step_metadata(ctx, b.n_q, b.n_kv, b.head_dim, d.q.device)
+    assert meta.prefill_ctas > 0 and meta.decode.num_ctas == ops.sm_count("cuda") - meta.prefill_ctas
+    plain = B200GqaBackend(b.n_q, b.n_kv, b.head_dim, b.scale, 1, "cuda", torch.bfloat16)
+    plain._overlap_mixed = False
+    ctx2 = ForwardContext(None, None, d.slot_mapping, d.block_table, b.cu_seqlens_q, b.seqlens_kv,
+                          None, plain, [d.kv_cache], False)
+    out2 = plain.paged_attention(0, d.q, d.k_new, d.v_new, ctx2).cpu()
+    assert cached_step_metadata(ctx2, b.n_q, b.n_kv, b.head_dim, d.q.device).prefill_ctas == 0
+    chunk_rows = slice(60, None)                      # the chunks' rows come from the same plan: same bits
+    assert torch.equal(out[chunk_rows], out2[chunk_rows])
+    assert_attention_close(out2, ref, what="config 2, one kernel after the other")
+    for _ in range(3):                                # repeated side by side steps on the pooled plans
+        again = backend.paged_attention(0, d.q, d.k_new, d.v_new, ForwardContext(
+            None, None, d.slot_mapping, d.block_table, b.cu_seqlens_q, b.seqlens_kv, None, backend,
+            [d.kv_cache], False)).cpu()
+        assert torch.equal(again, out)
+    assert ops.read_status("cuda") == 0

@@ -251,3 +251,19 @@ def test_mla_backend_slices_heads_beyond_one_launch():
     assert heads(24) == 12 and heads(20) == 10 and heads(17) == 1
     with pytest.raises(ValueError):
         heads(0)
+
+
+def test_mixed_step_split_model():
+    """The SM split of a mixed step: none when one side is missing or too small to matter, a
+    multiple of 8 otherwise, larger for more prefill work; and the scan that feeds it."""
+    from auto_infer_b200.metadata import mixed_split, scan_step
+    assert mixed_split(0, 1000, 148) == 0 and mixed_split(10 ** 9, 0, 148) == 0
+    assert mixed_split(10 ** 9, 3, 148) == 0                  # a sliver of prefill work: not worth a split
+    n = mixed_split(1_060_000_000, 8448, 148)                 # the mixed benchmark configuration
+    assert n % 8 == 0 and 40 <= n <= 72
+    assert mixed_split(1_060_000_000, 12000, 148) > n > mixed_split(1_060_000_000, 5000, 148) > 0
+    # 32 q / 8 kv heads: a 512-token chunk over a 1 024-token prefix and two decode rows
+    seqs, dec_bytes, tiles = scan_step([1, 513, 514], [100, 1536, 7], 32, 8, 128)
+    assert seqs == [1] and dec_bytes == (100 + 7) * 2 * 8 * 128 * 2
+    # items of 32 tokens (128 rows / group 4): item i sees keys up to 1024 + 32 i + 31
+    assert tiles == sum(((1024 + 32 * i + 31) // 128 + 1) for i in range(16)) * 8
