@@ -271,11 +271,11 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
       if (gw == 0) MLA_TRACE(1, it);
       const uint32_t sbase = smem_u32(sm.stage[s]);
 
-      // ---- this warp's quarter of S = Q K^T: 16 tokens x sub-tiles [sub0, sub1); two
+      // ---- this warp's quarter of S = Q K^T: 16 tokens x sub-tiles [sub0, sub1); four
       // accumulator sets per n-tile keep the dependent mma chain short
-      float part[2][2][4];
+      float part[4][2][4];
 #pragma unroll
-      for (int u = 0; u < 2; ++u)
+      for (int u = 0; u < 4; ++u)
 #pragma unroll
         for (int n = 0; n < 2; ++n) part[u][n][0] = part[u][n][1] = part[u][n][2] = part[u][n][3] = 0.f;
       // sub-tiles [0,5) or [5,9), 4 k-steps each.  The inline-asm loads and MMAs keep
@@ -295,16 +295,18 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
       for (int st = 0; st < 20; ++st) {
         if (st < nsteps) {
           if (st + 2 < nsteps) load_step(st + 2, (st + 2) % 3);
-          mma_bf16_16816(part[st & 1][0], qa[st % 3], kb[st % 3][0], kb[st % 3][1]);
-          mma_bf16_16816(part[st & 1][1], qa[st % 3], kb[st % 3][2], kb[st % 3][3]);
+          mma_bf16_16816(part[st & 3][0], qa[st % 3], kb[st % 3][0], kb[st % 3][1]);
+          mma_bf16_16816(part[st & 3][1], qa[st % 3], kb[st % 3][2], kb[st % 3][3]);
         }
       }
       float* my_part = sm.s_part[grp][(it >> 1) & 1][gw] + lane * 8;
 #pragma unroll
       for (int n = 0; n < 2; ++n)
         *reinterpret_cast<float4*>(my_part + n * 4) =
-            make_float4(part[0][n][0] + part[1][n][0], part[0][n][1] + part[1][n][1],
-                        part[0][n][2] + part[1][n][2], part[0][n][3] + part[1][n][3]);
+            make_float4((part[0][n][0] + part[1][n][0]) + (part[2][n][0] + part[3][n][0]),
+                        (part[0][n][1] + part[1][n][1]) + (part[2][n][1] + part[3][n][1]),
+                        (part[0][n][2] + part[1][n][2]) + (part[2][n][2] + part[3][n][2]),
+                        (part[0][n][3] + part[1][n][3]) + (part[2][n][3] + part[3][n][3]));
       if (gw == 0) MLA_TRACE(2, it);
       named_bar_sync(gbar, 128);
       if (gw == 0) MLA_TRACE(3, it);
