@@ -446,35 +446,35 @@ paged_mha_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constan
       }
       if (p.lse_out && (t & 7) == 0) p.lse_out[rix] = lse;
     }
-    return;
-  }
+  } else {
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int row = half ? r1 : r0;
-    if (row >= item.n_rows) continue;
-    const float l = half ? l1 : l0, m = half ? m1 : m0;
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    const float lse = l > 0.f ? m * p.scale + __logf(l) : -INFINITY;
-    const int64_t rix = (int64_t)(item.tok0 + row) * p.num_heads + item.head;
-    if (p.num_splits > 1) {
-      const int64_t prow = (int64_t)item.split * p.num_tokens * p.num_heads + rix;
-      float* dst = p.part_o + prow * kMhaVDim;
+    for (int half = 0; half < 2; ++half) {
+      const int row = half ? r1 : r0;
+      if (row >= item.n_rows) continue;
+      const float l = half ? l1 : l0, m = half ? m1 : m0;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float lse = l > 0.f ? m * p.scale + __logf(l) : -INFINITY;
+      const int64_t rix = (int64_t)(item.tok0 + row) * p.num_heads + item.head;
+      if (p.num_splits > 1) {
+        const int64_t prow = (int64_t)item.split * p.num_tokens * p.num_heads + rix;
+        float* dst = p.part_o + prow * kMhaVDim;
 #pragma unroll
-      for (int n = 0; n < kMhaVDim / 8; ++n)
-        *reinterpret_cast<float2*>(dst + n * 8 + qlane * 2) =
-            make_float2(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
-      if (qlane == 0) p.part_lse[prow] = lse;
-    } else {
+        for (int n = 0; n < kMhaVDim / 8; ++n)
+          *reinterpret_cast<float2*>(dst + n * 8 + qlane * 2) =
+              make_float2(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+        if (qlane == 0) p.part_lse[prow] = lse;
+      } else {
 #pragma unroll
-      for (int n = 0; n < kMhaVDim / 8; ++n) {
-        const float x = o[n][half * 2] * inv, y = o[n][half * 2 + 1] * inv;
-        const int64_t off = rix * kMhaVDim + n * 8 + qlane * 2;
-        if (p.out_is_f32)
-          *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + off) = make_float2(x, y);
-        else
-          *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pack_bf16(x, y);
+        for (int n = 0; n < kMhaVDim / 8; ++n) {
+          const float x = o[n][half * 2] * inv, y = o[n][half * 2 + 1] * inv;
+          const int64_t off = rix * kMhaVDim + n * 8 + qlane * 2;
+          if (p.out_is_f32)
+            *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.out) + off) = make_float2(x, y);
+          else
+            *reinterpret_cast<uint32_t*>(reinterpret_cast<__nv_bfloat16*>(p.out) + off) = pack_bf16(x, y);
+        }
+        if (p.lse_out && qlane == 0) p.lse_out[rix] = lse;
       }
-      if (p.lse_out && qlane == 0) p.lse_out[rix] = lse;
     }
   }
 }
