@@ -25,9 +25,12 @@ _PREFILL_US_PER_TILE = 1.26
 _DECODE_FIXED_US, _PREFILL_FIXED_US = 6.0, 4.0
 
 
-def mixed_split(decode_bytes: int, prefill_tiles: int, sms: int) -> int:
+def mixed_split(decode_bytes: int, prefill_tiles: int, sms: int, prefill_items: int = 0,
+                longest_item_tiles: int = 0) -> int:
     """SMs to give the wide-query kernel in a mixed step (a multiple of 8), or 0 when running the
-    two kernels one after the other on all SMs is expected to be as fast (within 7 %)."""
+    two kernels one after the other on all SMs is expected to be as fast (within 7 %).  The
+    wide-query kernel's work comes in items of 128 query rows (``prefill_items`` of them, the
+    longest ``longest_item_tiles`` tiles): with few items per SM the longest ones set its time."""
     if decode_bytes <= 0 or prefill_tiles <= 0 or sms < 32:
         return 0
 
@@ -35,7 +38,14 @@ def mixed_split(decode_bytes: int, prefill_tiles: int, sms: int) -> int:
         return decode_bytes / (min(_HBM_GBS, n * _DECODE_GBS_PER_SM) * 1e3) + _DECODE_FIXED_US
 
     def t_pre(n):
-        return prefill_tiles * _PREFILL_US_PER_TILE / n + _PREFILL_FIXED_US
+        tiles = prefill_tiles / n
+        if prefill_items and longest_item_tiles:
+            rounds = -(-prefill_items // n)
+            if rounds <= 2:                       # whole items, longest first: the last round sets the time
+                tiles = max(tiles, longest_item_tiles * rounds)
+            else:
+                tiles += longest_item_tiles / 2
+        return tiles * _PREFILL_US_PER_TILE + _PREFILL_FIXED_US
 
     one_after_the_other = t_dec(sms) + t_pre(sms)
     best_n, best_t = 0, one_after_the_other
@@ -49,9 +59,9 @@ def mixed_split(decode_bytes: int, prefill_tiles: int, sms: int) -> int:
 def scan_step(cu_seqlens_q, seqlens_kv, num_q_heads: int, num_kv_heads: int, head_dim: int,
               causal_base=None):
     """(indices of the sequences for the wide-query kernel, KV bytes the decode kernel reads,
-    128 x 128 tiles the wide-query kernel computes) of a step."""
+    128 x 128 tiles the wide-query kernel computes, its items, the longest item's tiles) of a step."""
     group = num_q_heads // num_kv_heads
-    prefill_seqs, decode_bytes, prefill_tiles = [], 0, 0
+    prefill_seqs, decode_bytes, prefill_tiles, prefill_items, longest = [], 0, 0, 0, 0
     prev = 0
     for b, end in enumerate(cu_seqlens_q):
         q_len, kv = int(end) - prev, int(seqlens_kv[b])
@@ -62,10 +72,13 @@ def scan_step(cu_seqlens_q, seqlens_kv, num_q_heads: int, num_kv_heads: int, hea
             tokens_per_item = max(1, 128 // group)
             for first in range(0, q_len, tokens_per_item):
                 last_key = min(base + min(first + tokens_per_item, q_len) - 1, kv - 1)
-                prefill_tiles += (last_key // 128 + 1 if last_key >= 0 else 0) * num_kv_heads
+                tiles = last_key // 128 + 1 if last_key >= 0 else 0
+                prefill_tiles += tiles * num_kv_heads
+                prefill_items += num_kv_heads
+                longest = max(longest, tiles)
         elif q_len > 0:
             decode_bytes += kv * 2 * num_kv_heads * head_dim * 2
-    return prefill_seqs, decode_bytes, prefill_tiles
+    return prefill_seqs, decode_bytes, prefill_tiles, prefill_items, longest
 
 
 class StepMetadata:
@@ -174,9 +187,10 @@ def step_metadata(ctx, num_q_heads: int, num_kv_heads: int, head_dim: int, devic
     if meta is None:
         prefill_ctas = 0
         if split_mixed and torch.device(device).type == "cuda":
-            _, decode_bytes, prefill_tiles = scan_step(ctx.cu_seqlens_q, ctx.seqlens_kv, num_q_heads,
-                                                       num_kv_heads, head_dim, causal_base)
-            prefill_ctas = mixed_split(decode_bytes, prefill_tiles, ops.sm_count(torch.device(device)))
+            _, decode_bytes, prefill_tiles, items, longest = scan_step(
+                ctx.cu_seqlens_q, ctx.seqlens_kv, num_q_heads, num_kv_heads, head_dim, causal_base)
+            prefill_ctas = mixed_split(decode_bytes, prefill_tiles, ops.sm_count(torch.device(device)),
+                                       items, longest)
         pool_key = key + (prefill_ctas,)           # a plan is built for one share of the SMs
         pooled = pool.get(pool_key) if pool is not None else None
         if pooled is not None and pooled.capacity_seqs >= len(ctx.cu_seqlens_q):

@@ -296,8 +296,8 @@ def side_config(name, device):
         # the step as the backend runs it: the two kernels side by side on disjoint SMs (the decode
         # plan built for its share), when the cost model expects a gain
         from auto_infer_b200.metadata import mixed_split, scan_step
-        _, dec_b, pre_t = scan_step(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim)
-        n_pre = mixed_split(dec_b, pre_t, ops.sm_count(device))
+        _, dec_b, pre_t, pre_items, pre_longest = scan_step(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim)
+        n_pre = mixed_split(dec_b, pre_t, ops.sm_count(device), pre_items, pre_longest)
         us, best = us_seq, us_seq
         if n_pre:
             split = StepMetadata(b.cu_seqlens_q, b.seqlens_kv, b.n_q, b.n_kv, b.head_dim, device,

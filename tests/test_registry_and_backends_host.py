@@ -263,7 +263,12 @@ def test_mixed_step_split_model():
     assert n % 8 == 0 and 40 <= n <= 72
     assert mixed_split(1_060_000_000, 12000, 148) > n > mixed_split(1_060_000_000, 5000, 148) > 0
     # 32 q / 8 kv heads: a 512-token chunk over a 1 024-token prefix and two decode rows
-    seqs, dec_bytes, tiles = scan_step([1, 513, 514], [100, 1536, 7], 32, 8, 128)
+    seqs, dec_bytes, tiles, items, longest = scan_step([1, 513, 514], [100, 1536, 7], 32, 8, 128)
     assert seqs == [1] and dec_bytes == (100 + 7) * 2 * 8 * 128 * 2
     # items of 32 tokens (128 rows / group 4): item i sees keys up to 1024 + 32 i + 31
     assert tiles == sum(((1024 + 32 * i + 31) // 128 + 1) for i in range(16)) * 8
+    assert items == 16 * 8 and longest == (1024 + 511) // 128 + 1
+    # few long items: a share of the SMs that needs a second round of items is not worth it
+    # (16 decode rows of 2 600 tokens beside ONE 512-token chunk over an 8 192-token prefix)
+    _, db, pt, it, lg = scan_step(list(range(1, 17)) + [16 + 512], [2600] * 16 + [8192 + 512], 32, 8, 128)
+    assert it == 128 and mixed_split(db, pt, 148, it, lg) == 0 and mixed_split(db, pt, 148) > 0
