@@ -12,8 +12,8 @@ functions of ``torch_npu`` it imports inside its layers:
 
 ``install()`` registers this module as ``torch_npu``, aliases ``torch.npu`` to ``torch.cuda``
 and points ``auto_infer.platform.npu_device`` at a CUDA device.  With that, the reference's
-``GqaFIABackend`` (mode "paged") runs on the kernels of this package through the very
-calls it already makes: the two paged operators go to the C-ABI library, the three small
+``GqaFIABackend`` and ``MlaFIABackend`` (mode "paged"; MLA in its default non-absorbed form)
+run on the kernels of this package through the very calls they already make: the two paged operators go to the C-ABI library, the three small
 elementwise operators to plain torch (they are outside the attention path and not what
 this package accelerates).  The families registered by ``install_into_auto_infer()`` are the
 faster way in (one plan per step instead of one per layer call, fused prologue); the shim is
@@ -54,6 +54,18 @@ def _step_plan(actual_seq_q: Sequence[int], actual_seq_kv: Sequence[int], num_he
     return meta
 
 
+def _mha_plan(actual_seq_q: Sequence[int], actual_seq_kv: Sequence[int], num_heads: int, device):
+    """As ``_step_plan``, for the K-192 / V-128 multi-head kernel."""
+    key = ("mha", tuple(int(c) for c in actual_seq_q), tuple(int(k) for k in actual_seq_kv), num_heads, str(device))
+    plan = _plan_cache.get(key)
+    if plan is None:
+        if len(_plan_cache) >= 8:
+            _plan_cache.pop(next(iter(_plan_cache)))
+        plan = ops.MhaPlan(key[1], key[2], num_heads, device)
+        _plan_cache[key] = plan
+    return plan
+
+
 def npu_fused_infer_attention_score(query, key, value, *, block_table, input_layout="TND", block_size,
                                     actual_seq_lengths, actual_seq_lengths_kv, num_key_value_heads,
                                     num_heads, scale, atten_mask=None, sparse_mode=3):
@@ -70,8 +82,16 @@ def npu_fused_infer_attention_score(query, key, value, *, block_table, input_lay
     if key.shape[1] != block_size or key.shape[2] != num_key_value_heads * d:
         raise ValueError("key must be the (num_blocks, block_size, num_kv_heads * head_dim) cache view")
     if value.shape[2] != num_key_value_heads * d:
-        raise NotImplementedError("value rows as wide as key rows (the GQA caches); the MLA families "
-                                  "are served by B200MlaBackend, not by this shim")
+        # the non-absorbed MLA call of MlaFIABackend._attn (auto_infer/layers/attention/mla.py:247-255):
+        # one kv head per query head, K rows 192 wide, V rows 128 wide
+        dv = value.shape[2] // num_key_value_heads
+        if num_key_value_heads != num_heads or (d, dv) != (192, 128) or value.shape[2] != num_heads * dv:
+            raise NotImplementedError("unequal K / V widths are served for the non-absorbed MLA shape only "
+                                      "(one kv head per query head, K 192 / V 128)")
+        plan = _mha_plan(actual_seq_lengths, actual_seq_lengths_kv, num_heads, query.device)
+        out = ops.paged_mha(query, key.view(num_blocks, block_size, num_heads, d),
+                            value.view(num_blocks, block_size, num_heads, dv), block_table, plan, scale)
+        return out, None
     k4 = key.view(num_blocks, block_size, num_key_value_heads, d)
     v4 = value.view(num_blocks, block_size, num_key_value_heads, d)
     meta = _step_plan(actual_seq_lengths, actual_seq_lengths_kv, num_heads, num_key_value_heads, d,

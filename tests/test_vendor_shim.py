@@ -86,3 +86,49 @@ def test_paged_operators_with_the_reference_call_shapes():
     assert_attention_close(out.cpu(), ref, what="vendor-op call shape")
     assert len(torch_npu._plan_cache) >= 1
     assert ops.read_status("cuda") == 0
+
+
+@pytest.mark.gpu
+def test_non_absorbed_mla_call_shape():
+    """What MlaFIABackend._write_kv / ._attn do in the default, non-absorbed form
+    (auto_infer/layers/attention/mla.py:243-255): K rows 192 wide, V rows 128 wide, one kv head
+    per query head, a decode row and a prefill chunk in one step."""
+    from auto_infer_b200 import ops
+    from auto_infer_b200 import vendor_shim as torch_npu
+    from tests.paging import page_out
+    from tests.parity import assert_attention_close
+    g = torch.Generator().manual_seed(8)
+    nh, bs = 4, 16
+    seqs = [(1, 300), (70, 70), (2, 65)]
+    lens = [kv for _, kv in seqs]
+    k = torch.randn(sum(lens), nh, 192, generator=g).to(torch.bfloat16)
+    v = torch.randn(sum(lens), nh, 128, generator=g).to(torch.bfloat16)
+    q = torch.randn(sum(ql for ql, _ in seqs), nh, 192, generator=g).to(torch.bfloat16)
+    k_cache, v_cache, table, slots = page_out(k, v, lens, bs, 9)
+    # the step's own rows arrive through the slot write, as in the reference
+    new_rows, cu, at = [], [], 0
+    for ql, kv in seqs:
+        new_rows += list(range(at + kv - ql, at + kv))
+        at += kv
+        cu.append((cu[-1] if cu else 0) + ql)
+    kc, vc = k_cache.clone(), v_cache.clone()
+    new_slots = [slots[i] for i in new_rows]
+    kc.view(-1, nh, 192)[new_slots] = 0
+    vc.view(-1, nh, 128)[new_slots] = 0
+    kc, vc = kc.cuda(), vc.cuda()
+    torch_npu._npu_reshape_and_cache(key=k[new_rows].cuda(), value=v[new_rows].cuda(), key_cache=kc, value_cache=vc,
+                                     slot_indices=torch.tensor(new_slots, dtype=torch.int32, device="cuda"))
+    assert torch.equal(kc.cpu(), k_cache) and torch.equal(vc.cpu(), v_cache)
+    nb = kc.shape[0]
+    out, _ = torch_npu.npu_fused_infer_attention_score(
+        query=q.cuda(), key=kc.view(nb, bs, nh * 192), value=vc.view(nb, bs, nh * 128), block_table=table.cuda(),
+        input_layout="TND", block_size=bs, actual_seq_lengths=cu, actual_seq_lengths_kv=lens,
+        num_key_value_heads=nh, num_heads=nh, scale=192 ** -0.5, atten_mask=None, sparse_mode=3)
+    ref = orc.paged_attention(q, k_cache, v_cache, table, cu, lens, 192 ** -0.5)
+    assert_attention_close(out.cpu(), ref, what="non-absorbed MLA call shape")
+    with pytest.raises(NotImplementedError):                  # any other unequal widths
+        torch_npu.npu_fused_infer_attention_score(
+            query=q.cuda(), key=kc.view(nb, bs, nh * 192), value=vc.view(nb, bs, nh * 128)[..., :nh * 64].contiguous(),
+            block_table=table.cuda(), input_layout="TND", block_size=bs, actual_seq_lengths=cu,
+            actual_seq_lengths_kv=lens, num_key_value_heads=nh, num_heads=nh, scale=1.0)
+    assert ops.read_status("cuda") == 0
