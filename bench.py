@@ -761,7 +761,15 @@ def main():
         verify_how = f"verification did not run: {exc!r}"
 
     # ---- end to end through the backend call with host buffers -------------
-    backend = B200GqaBackend(b.n_q, b.n_kv, b.head_dim, b.scale, 1, device, torch.bfloat16)
+    # one backend object per staging set: each keeps its own refillable plan, so the plan of
+    # step k + 1 can travel while the kernels of step k still read theirs
+    from auto_infer_b200.metadata import step_metadata
+    # (context parallel: two attention objects over the one peer exchange, for the same reason)
+    cpds = [cpd]
+    if world > 1:
+        cpds.append(ContextParallelDecode(b.cu_seqlens_q, global_kv, b.n_q, b.n_kv, b.head_dim, b.block_size,
+                                          device, cp_rank=rank, cp_size=world, exchange=exchange))
+    backends = [B200GqaBackend(b.n_q, b.n_kv, b.head_dim, b.scale, 1, device, torch.bfloat16) for _ in range(2)]
     # The step's inputs live in one pinned staging arena on the host (as an engine's input
     # stager keeps them) and travel in one copy; the tensors below are views into it.
     srcs = {k: getattr(b, k).cpu().contiguous() for k in ("q", "k_new", "v_new", "slot_mapping", "block_table")}
@@ -770,7 +778,8 @@ def main():
         offs[k] = total
         total += (v.numel() * v.element_size() + 255) // 256 * 256
     host_arena = torch.empty(total, dtype=torch.uint8).pin_memory()
-    dev_arena = torch.empty(total, dtype=torch.uint8, device=device)
+    depth = 2
+    dev_arenas = [torch.empty(total, dtype=torch.uint8, device=device) for _ in range(depth)]
 
     def _view(arena, k):
         v = srcs[k]
@@ -780,18 +789,19 @@ def main():
     host = {k: _view(host_arena, k) for k in srcs}
     for k in srcs:
         host[k].copy_(srcs[k])
-    dev = {k: _view(dev_arena, k) for k in srcs}
+    devs = [{k: _view(arena, k) for k in srcs} for arena in dev_arenas]
     h2d = sum(v.numel() * v.element_size() for v in host.values())
-    # Two result buffers on the host: step k's device -> host copy is awaited when its buffer
-    # comes up for reuse (step k + 2), as an engine's output thread reads results while the
-    # next step is already being planned and launched.  Every step still copies its inputs
-    # in and its result out inside the timed region, and the region ends with all results
-    # on the host.
-    depth = 2
+    # Two staging sets (device input arena, pinned result buffer) and two copy streams, as an
+    # engine's input stager and output thread work: step k + 1's inputs travel while step k's
+    # kernels run, step k's result travels while step k + 1's kernels run, and a set is reused
+    # when its result has reached the host (step k + 2).  Every step still copies its inputs in
+    # and its result out inside the timed region, and the region ends with all results on the
+    # host.
     out_hosts = [torch.empty(b.q.shape, dtype=torch.bfloat16).pin_memory() for _ in range(depth)]
     out_done = [None] * depth
     d2h = out_hosts[0].numel() * out_hosts[0].element_size()
     e2e_count = [0]
+    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
 
     def e2e_step():
         # a step as the engine drives it: inputs from the host, this step's lengths planned on
@@ -799,20 +809,35 @@ def main():
         i = e2e_count[0] % depth
         e2e_count[0] += 1
         if out_done[i] is not None:
-            out_done[i].synchronize()
-        dev_arena.copy_(host_arena, non_blocking=True)
+            out_done[i].synchronize()                # set i is free: its result is on the host
+        dev = devs[i]
+        cur = torch.cuda.current_stream(device)
+        arrived, computed, done = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+        backend = backends[i]
+        ctx = None
+        with torch.cuda.stream(copy_in):             # the step's plan is built and uploaded beside its inputs
+            dev_arenas[i].copy_(host_arena, non_blocking=True)
+            if world == 1:
+                ctx = ForwardContext(None, None, dev["slot_mapping"], dev["block_table"],
+                                     b.cu_seqlens_q, b.seqlens_kv, None, backend, [b.kv_cache], True)
+                step_metadata(ctx, b.n_q, b.n_kv, b.head_dim, device, pool=backend._meta_pool,
+                              split_mixed=backend._overlap_mixed)
+            else:
+                cpds[i].replan(b.cu_seqlens_q, global_kv)
+            arrived.record(copy_in)
+        cur.wait_event(arrived)
         if world == 1:
-            ctx = ForwardContext(None, None, dev["slot_mapping"], dev["block_table"],
-                                 b.cu_seqlens_q, b.seqlens_kv, None, backend, [b.kv_cache], True)
             o = backend.paged_attention(0, dev["q"], dev["k_new"], dev["v_new"], ctx)
         else:
-            cpd.replan(b.cu_seqlens_q, global_kv)
             if owner_of_new_token:
                 ops.reshape_and_cache(dev["k_new"], dev["v_new"], k_cache, v_cache, dev["slot_mapping"])
-            o = cpd.attend(dev["q"], k_cache, v_cache, dev["block_table"], b.scale)
-        out_hosts[i].copy_(o, non_blocking=True)
-        done = torch.cuda.Event()
-        done.record()
+            o = cpds[i].attend(dev["q"], k_cache, v_cache, dev["block_table"], b.scale)
+        computed.record(cur)
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(computed)
+            out_hosts[i].copy_(o, non_blocking=True)
+            o.record_stream(copy_out)
+            done.record(copy_out)
         out_done[i] = done
 
     def e2e_drain():
@@ -875,7 +900,7 @@ def main():
                          "frac_of_nominal_8tbs": achieved / 8000.0,
                          "timed": "same graph replay as the step, the attention kernel alone"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "copies": "on two copy streams, overlapped with the neighbouring steps' kernels",
                     "results_in_flight": depth},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "device_status": status,
