@@ -801,7 +801,23 @@ def main():
     out_done = [None] * depth
     d2h = out_hosts[0].numel() * out_hosts[0].element_size()
     e2e_count = [0]
-    copy_in, copy_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    # Copy streams pay when the device step is long against the host's own work per step; a
+    # step of ~100 us (eight ranks) is bound by the host, where two more stream switches per
+    # step cost more than the copies they hide: there everything stays on one stream.
+    overlap_copies = ms_per_step > 0.15               # the same on all ranks (max over ranks)
+    main_stream = torch.cuda.current_stream(device)
+    copy_in = torch.cuda.Stream(device) if overlap_copies else main_stream
+    copy_out = torch.cuda.Stream(device) if overlap_copies else main_stream
+
+    def e2e_compute(i, dev, ctx):
+        if world == 1:
+            if ctx is None:
+                ctx = ForwardContext(None, None, dev["slot_mapping"], dev["block_table"],
+                                     b.cu_seqlens_q, b.seqlens_kv, None, backends[i], [b.kv_cache], True)
+            return backends[i].paged_attention(0, dev["q"], dev["k_new"], dev["v_new"], ctx)
+        if owner_of_new_token:
+            ops.reshape_and_cache(dev["k_new"], dev["v_new"], k_cache, v_cache, dev["slot_mapping"])
+        return cpds[i].attend(dev["q"], k_cache, v_cache, dev["block_table"], b.scale)
 
     def e2e_step():
         # a step as the engine drives it: inputs from the host, this step's lengths planned on
@@ -811,28 +827,30 @@ def main():
         if out_done[i] is not None:
             out_done[i].synchronize()                # set i is free: its result is on the host
         dev = devs[i]
-        cur = torch.cuda.current_stream(device)
-        arrived, computed, done = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
-        backend = backends[i]
+        done = torch.cuda.Event()
+        if not overlap_copies:                       # everything in order on the compute stream
+            dev_arenas[i].copy_(host_arena, non_blocking=True)
+            if world > 1:
+                cpds[i].replan(b.cu_seqlens_q, global_kv)
+            out_hosts[i].copy_(e2e_compute(i, dev, None), non_blocking=True)
+            done.record()
+            out_done[i] = done
+            return
+        arrived, computed = torch.cuda.Event(), torch.cuda.Event()
         ctx = None
         with torch.cuda.stream(copy_in):             # the step's plan is built and uploaded beside its inputs
             dev_arenas[i].copy_(host_arena, non_blocking=True)
             if world == 1:
                 ctx = ForwardContext(None, None, dev["slot_mapping"], dev["block_table"],
-                                     b.cu_seqlens_q, b.seqlens_kv, None, backend, [b.kv_cache], True)
-                step_metadata(ctx, b.n_q, b.n_kv, b.head_dim, device, pool=backend._meta_pool,
-                              split_mixed=backend._overlap_mixed)
+                                     b.cu_seqlens_q, b.seqlens_kv, None, backends[i], [b.kv_cache], True)
+                step_metadata(ctx, b.n_q, b.n_kv, b.head_dim, device, pool=backends[i]._meta_pool,
+                              split_mixed=backends[i]._overlap_mixed)
             else:
                 cpds[i].replan(b.cu_seqlens_q, global_kv)
             arrived.record(copy_in)
-        cur.wait_event(arrived)
-        if world == 1:
-            o = backend.paged_attention(0, dev["q"], dev["k_new"], dev["v_new"], ctx)
-        else:
-            if owner_of_new_token:
-                ops.reshape_and_cache(dev["k_new"], dev["v_new"], k_cache, v_cache, dev["slot_mapping"])
-            o = cpds[i].attend(dev["q"], k_cache, v_cache, dev["block_table"], b.scale)
-        computed.record(cur)
+        main_stream.wait_event(arrived)
+        o = e2e_compute(i, dev, ctx)
+        computed.record(main_stream)
         with torch.cuda.stream(copy_out):
             copy_out.wait_event(computed)
             out_hosts[i].copy_(o, non_blocking=True)
@@ -900,7 +918,8 @@ def main():
                          "frac_of_nominal_8tbs": achieved / 8000.0,
                          "timed": "same graph replay as the step, the attention kernel alone"},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "copies": "on two copy streams, overlapped with the neighbouring steps' kernels",
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "copies": ("on two copy streams, overlapped with the neighbouring steps' kernels" if overlap_copies
+                               else "on the compute stream (host-bound step)"),
                     "results_in_flight": depth},
             "gpu_launches": launches_per_step * args.steps,
             "clocks": clocks, "device_status": status,
