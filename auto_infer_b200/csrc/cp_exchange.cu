@@ -79,6 +79,7 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t w) {
 
 __global__ void __launch_bounds__(kExThreads)
 cp_exchange_combine_kernel(const ExchangeParams p) {
+  grid_dep_launch();                                 // the next kernel may set itself up meanwhile (it waits for this grid itself)
   grid_dep_wait();                                   // the local record comes from the decode kernel
   const uint32_t seq = p.state[0] + 1;               // advanced at the very end by the last block
   const int slot = seq & 1u;

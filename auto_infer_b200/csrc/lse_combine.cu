@@ -10,6 +10,7 @@ __global__ void __launch_bounds__(256)
 lse_combine_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts,
                    int64_t stride_o, int64_t stride_lse, int n_parts, int64_t rows, int dim,
                    void* __restrict__ out, int out_is_f32, float* __restrict__ lse_out) {
+  grid_dep_launch();              // the next kernel may set itself up meanwhile (it waits for this grid itself)
   grid_dep_wait();                // the parts come from the kernel (or collective) before this one
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;

@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(128)
 split_merge_kernel(const int32_t* __restrict__ plan, const float* __restrict__ part_o,
                    const float* __restrict__ part_lse, void* __restrict__ out,
                    float* __restrict__ lse_out, int num_q_heads, int group, int out_is_f32) {
+  grid_dep_launch();                                 // the next kernel may set itself up meanwhile (it waits for this grid itself)
   grid_dep_wait();                                   // the partial records come from the decode kernel
   constexpr int kRowsPerCta = 512 / kDim;            // 1 (MLA) or 4 (GQA)
   constexpr int kThreadsPerRow = kDim / 4;
