@@ -50,6 +50,7 @@ struct GqaRopeParams {
 // i.e. the same registers of lane l ^ 16.
 __global__ void __launch_bounds__(256)
 gqa_rope_cache_kernel(const GqaRopeParams p) {
+  grid_dep_launch();              // the attention kernel may set itself up meanwhile (it waits for this grid itself)
   grid_dep_wait();
   const int lane = threadIdx.x & 31;
   const int heads = p.num_q_heads + p.num_kv_heads;
@@ -142,6 +143,7 @@ __device__ __forceinline__ void rope_interleaved_pair(float even, float odd, flo
 
 __global__ void __launch_bounds__(256)
 mla_rope_norm_cache_kernel(const MlaRopeParams p) {
+  grid_dep_launch();              // the attention kernel may set itself up meanwhile (it waits for this grid itself)
   grid_dep_wait();
   const int lane = threadIdx.x & 31;
   const int rows_per_token = p.num_heads + 1;                  // every head's q_pe, then the latent row
