@@ -136,6 +136,28 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap lat_map, const MlaParams p
   }
   __syncthreads();
   MLA_CTA_TRACE(0, global_timer_ns());
+  // While the kernels in front drain (the previous layer's merge, this step's slot write): the
+  // first tiles of this CTA's first item are asked into L2 (hints only: block ids read past the
+  // L1 and used for nothing but the prefetch addresses; the loads proper follow the dependency
+  // wait and find a warm L2).
+  if (warp == kMlaWarps && item_begin < item_end) {
+    constexpr int kHintTiles = 3;
+    const DecodeItem& f = cta_rec->first;
+    const int nbox = p.boxes_per_tile;
+    const int n_hint = min(f.tile_end - f.tile_begin, kHintTiles) * nbox;
+    if (lane < n_hint && f.kv_len > 0) {
+      const int tile = f.tile_begin + lane / nbox, box = lane % nbox;
+      int lb = ((tile * kMlaTileTokens) >> p.block_shift) + box;
+      const int last_block = (f.kv_len - 1) >> p.block_shift;
+      lb = lb > last_block ? last_block : lb;
+      const int bid = __ldcg(p.block_table + (int64_t)f.seq * p.bt_stride + lb);
+      if (bid >= 0 && bid < p.num_blocks) {
+        const int tok = (tile * kMlaTileTokens + box * p.box_tokens) & (p.block_size - 1);
+#pragma unroll
+        for (int c = 0; c < kMlaSub; ++c) tma_prefetch_4d(&lat_map, c * 64, 0, tok, bid);
+      }
+    }
+  }
   grid_dep_launch();              // the merge kernel may be scheduled; it waits for this grid itself
   grid_dep_wait();                // q and the step's new latent rows come from earlier kernels
   MLA_CTA_TRACE(1, global_timer_ns());
