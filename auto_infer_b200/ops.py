@@ -69,11 +69,18 @@ def read_status(device, clear: bool = True) -> int:
     return value
 
 
+_sm_counts: dict = {}
+
+
 def sm_count(device=None) -> int:
-    if device is not None:
-        with torch.cuda.device(device):
-            return _lib.load().b200_sm_count()
-    return _lib.load().b200_sm_count()
+    """SMs of ``device`` (the current one by default); asked once per device."""
+    key = torch.device(device).index if device is not None else None
+    if key is None:
+        key = torch.cuda.current_device()
+    if key not in _sm_counts:
+        with torch.cuda.device(key):
+            _sm_counts[key] = _lib.load().b200_sm_count()
+    return _sm_counts[key]
 
 
 # --------------------------------------------------------------------------- #
@@ -182,9 +189,13 @@ class DecodePlan:
     def _upload(self, used: int) -> None:
         self.dev[:used].copy_(self.host[:used], non_blocking=True)
         if self.replayable:
-            done = torch.cuda.Event()
-            done.record(torch.cuda.current_stream(self.device))
-            self._copied[self._flip] = done
+            done = self._copied[self._flip]
+            if done is None:                         # one event per staging buffer, recorded again each time
+                done = self._copied[self._flip] = torch.cuda.Event()
+            if self.device.index is None or torch.cuda.current_device() == self.device.index:
+                done.record()                        # the current stream, where the copy was issued
+            else:
+                done.record(torch.cuda.current_stream(self.device))
 
     def refill(self, cu_seqlens_q: Sequence[int], seqlens_kv: Sequence[int],
                causal_base: Optional[Sequence[int]] = None) -> None:
